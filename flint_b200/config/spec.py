@@ -66,3 +66,12 @@ class ModelSpec:
     embed_additions: tuple = ()
     # Where the checkpoint calls a tensor otherwise than the parts do: the parts' name -> the stored name.
     stored_names: dict = field(default_factory=dict)
+    # A norm of the embedded rows (a PartSpec of the norm registry); its tensors live under ``embed_norm_name``.
+    embed_norm: PartSpec | None = None
+    embed_norm_name: str = "embed_norm."
+    # What a call of the run order hands on is a learned weighted sum of the embedded rows and the results of all
+    # calls so far: call i stores ``depth_mix_name`` [i + 2] under its layer's prefix (weights of X_0 .. X_(i+1)).
+    depth_mix: bool = False
+    depth_mix_name: str = "dwa"
+    # logits <- c tanh(logits / c) (0: as they are)
+    logit_softcap: float = 0.0

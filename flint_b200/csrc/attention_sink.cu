@@ -2,7 +2,8 @@
 // request's first tokens, and a learned sink logit per query head in the softmax's denominator.
 //
 // A query row t at position p of request slot[t] sees key j of its request if j <= p and (p - j < window or
-// j < keep_first); window 0: every j <= p.  The seen keys are numbered without gaps: first the kept ones below
+// j < keep_first); window 0: every j <= p.  Instead of a window a layer may cut the sequence into runs of `run`
+// positions counted from 0: then j is seen if j <= p and floor(j / run) = floor(p / run).  The seen keys are numbered without gaps: first the kept ones below
 // the window's start (positions 0 .. min(keep_first, lo) - 1, lo = max(0, p + 1 - window)), then lo .. p; a split
 // of the key range is a run of these numbers.  Kept tokens keep their positions: they were rotated where they
 // stand, and nothing is rotated again.  With a sink s_h the weights are e^(score_j - M) / (sum_j e^(score_j - M)
@@ -109,7 +110,7 @@ __global__ void __launch_bounds__(WARPS * 32, DPL <= 4 ? 6 : 3)
 sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                       const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ pos,
                       const int* __restrict__ slot, TO* __restrict__ out, float* __restrict__ scratch, int T, int nq,
-                      int nkv, int hd, int vd, int window, int keep_first, const float* __restrict__ sinks, float scale,
+                      int nkv, int hd, int vd, int window, int keep_first, int run, const float* __restrict__ sinks, float scale,
                       int split_keys, int n_splits, int g_chunks, const int* __restrict__ row_list) {
   extern __shared__ float smem[];  // per warp: GC * hd floats of q
   pdl_launch();
@@ -126,7 +127,8 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
   const int t = row_list ? row_list[ti] : ti;        // row of the batch
   const int G = nq / nkv, g0 = gchunk * GC, ng = min(GC, G - g0), h0 = kvh * G + g0;
   const int p = pos[t];
-  const int lo = window > 0 ? max(0, p + 1 - window) : 0;
+  // the first key of the stretch that ends at p: the window's start, or the start of p's run of `run` positions
+  const int lo = run > 0 ? (p / run) * run : (window > 0 ? max(0, p + 1 - window) : 0);
   const int n_first = min(keep_first, lo);              // kept keys below the window's start
   const int total = n_first + (p + 1 - lo);             // seen keys, numbered 0 .. total - 1
   const int u_lo = split * split_keys, u_hi = min(total, u_lo + split_keys);
@@ -329,7 +331,7 @@ __global__ void __launch_bounds__(128)
 sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                           const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table, int max_pages,
                           int page_size, const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int nq, int nkv, int hd,
-                          int vd, int window, int keep_first, const float* __restrict__ sinks, float scale) {
+                          int vd, int window, int keep_first, int run, const float* __restrict__ sinks, float scale) {
   extern __shared__ __align__(16) unsigned char sm_raw[];
   const int ldk = hd + 8, ldv = vd + 8;
   // two stages, each keys [MK][ldk], values [MK][ldv] and the keys' positions [MK] (or -1); the first stage's keys
@@ -363,8 +365,8 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
   __syncthreads();          // the query tile's place is free for keys
 
   const int p_last = p0 + n_rows - 1;
-  const int lo_first = window > 0 ? max(0, p0 + 1 - window) : 0;
-  const bool gap = window > 0 && lo_first > keep_first;               // kept keys and window do not touch
+  const int lo_first = run > 0 ? (p0 / run) * run : (window > 0 ? max(0, p0 + 1 - window) : 0);
+  const bool gap = (window > 0 || run > 0) && lo_first > keep_first;  // kept keys and window do not touch
   const int n_first = gap ? keep_first : 0, base = gap ? lo_first : 0;
   const int total = n_first + (p_last + 1 - base);
   const int* bt = block_table + (size_t)slot * max_pages;
@@ -439,7 +441,8 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
     // mask, scale, and this tile's maxima of the thread's two rows.  Most tiles lie behind every row of the tile and
     // inside every row's window: they need no mask
     float mx[2] = {-INFINITY, -INFINITY};
-    const bool interior = kpos[MK - 1] >= 0 && kpos[MK - 1] <= p0 && (window == 0 || p_last - kpos[0] < window);
+    const bool interior = kpos[MK - 1] >= 0 && kpos[MK - 1] <= p0 && (window == 0 || p_last - kpos[0] < window) &&
+                          (run == 0 || kpos[0] >= (p_last / run) * run);
     if (interior) {
 #pragma unroll
       for (int nt = 0; nt < MK / 8; ++nt)
@@ -454,7 +457,8 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int j = kpos[nt * 8 + 2 * tq + (e & 1)], rs = e >> 1, p = p_row[rs];
-          const bool ok = j >= 0 && row_ok[rs] && j <= p && (window == 0 || p - j < window || j < keep_first);
+          const bool ok = j >= 0 && row_ok[rs] && j <= p && (window == 0 || p - j < window || j < keep_first) &&
+                          (run == 0 || j >= (p / run) * run);
           s[nt][e] = ok ? s[nt][e] * scale : -INFINITY;
           mx[rs] = fmaxf(mx[rs], s[nt][e]);
         }
@@ -550,15 +554,16 @@ extern "C" int flint_qkv_write(const float* qkv, int n_partials, long long parti
 extern "C" int flint_sink_attention(const void* q, int q_dtype, const void* k_cache, const void* v_cache, int cache_dtype,
                                     const int* block_table, int max_pages, int page_size, const int* pos,
                                     const int* slot, void* out, int T, int nq, int nkv, int hd, int vd, int window,
-                                    int keep_first, const float* sinks, float scale, int split_keys, int n_splits,
-                                    float* scratch, const int* row_list, cudaStream_t stream) {
+                                    int keep_first, int run, const float* sinks, float scale, int split_keys,
+                                    int n_splits, float* scratch, const int* row_list, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd < 1 || vd < 1 || hd > 256 || vd > 32 * MAX_DPL)
     return fail("sink_attention: head sizes %d (keys) and %d (values) are not supported (1 to 256)", hd, vd);
   if (nkv <= 0 || nq % nkv) return fail("sink_attention: %d query heads do not divide into %d kv heads", nq, nkv);
   if (n_splits < 1 || split_keys < 1) return fail("sink_attention: bad split (%d keys, %d splits)", split_keys, n_splits);
   if (n_splits > 1 && !scratch) return fail("sink_attention: splits need scratch memory");
-  if (window < 0 || keep_first < 0) return fail("sink_attention: bad window");
+  if (window < 0 || keep_first < 0 || run < 0 || (run > 0 && (window > 0 || keep_first > 0)))
+    return fail("sink_attention: bad window (a run length excludes a window and kept first tokens)");
   const int elem = cache_dtype == FLINT_F32 ? 4 : 2;
   if ((hd % 8) == 0 && (((uintptr_t)k_cache) & 15)) return fail("sink_attention: the key cache must start on 16 bytes");
   (void)elem;
@@ -571,7 +576,7 @@ extern "C" int flint_sink_attention(const void* q, int q_dtype, const void* k_ca
 #define LAUNCH_D(TQ, TC, DPL)                                                                                         \
   launch_pdl(sink_attention_kernel<TQ, TC, TQ, DPL>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream, (const TQ*)q, \
              (const TC*)k_cache, (const TC*)v_cache, block_table, max_pages, page_size, pos, slot, (TQ*)out, scratch, T, \
-             nq, nkv, hd, vd, window, keep_first, sinks, scale, split_keys, n_splits, g_chunks, row_list)
+             nq, nkv, hd, vd, window, keep_first, run, sinks, scale, split_keys, n_splits, g_chunks, row_list)
 #define LAUNCH(TQ, TC)                                                     \
   do {                                                                     \
     if (vd <= 64) LAUNCH_D(TQ, TC, 2);                                     \
@@ -594,13 +599,14 @@ extern "C" int flint_sink_attention(const void* q, int q_dtype, const void* k_ca
 // out; head sizes in multiples of 16 up to 128.
 extern "C" int flint_sink_attention_tiles(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                                           int max_pages, int page_size, const int* tiles, int n_tiles, void* out, int nq,
-                                          int nkv, int hd, int vd, int window, int keep_first, const float* sinks,
-                                          float scale, cudaStream_t stream) {
+                                          int nkv, int hd, int vd, int window, int keep_first, int run,
+                                          const float* sinks, float scale, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (hd < 16 || vd < 16 || hd % 16 || vd % 16 || hd > 128 || vd > 128)
     return fail("sink_attention_tiles: head sizes %d and %d (multiples of 16 up to 128)", hd, vd);
   if (nkv <= 0 || nq % nkv) return fail("sink_attention_tiles: %d query heads do not divide into %d kv heads", nq, nkv);
-  if (window < 0 || keep_first < 0 || page_size <= 0) return fail("sink_attention_tiles: bad window or page size");
+  if (window < 0 || keep_first < 0 || page_size <= 0 || run < 0 || (run > 0 && (window > 0 || keep_first > 0)))
+    return fail("sink_attention_tiles: bad window or page size");
   if ((long long)n_tiles * nq > 0x7fffffffLL) return fail("sink_attention_tiles: too many work items");
   const size_t smem = 2 * ((size_t)MK * ((hd + 8) + (vd + 8)) * 2 + MK * sizeof(int));       // two stages
   const dim3 grid((unsigned)(n_tiles * nq)), block(128);
@@ -613,10 +619,10 @@ extern "C" int flint_sink_attention_tiles(const void* q, const void* k_cache, co
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_cache, *vv = (const __nv_bfloat16*)v_cache;
   if (hd <= 64 && vd <= 64)
     launch_pdl(sink_attention_mma_kernel<4, 8>, grid, block, smem, stream, qq, kk, vv, block_table, max_pages, page_size, tiles,
-               (__nv_bfloat16*)out, nq, nkv, hd, vd, window, keep_first, sinks, scale);
+               (__nv_bfloat16*)out, nq, nkv, hd, vd, window, keep_first, run, sinks, scale);
   else
     launch_pdl(sink_attention_mma_kernel<8, 16>, grid, block, smem, stream, qq, kk, vv, block_table, max_pages, page_size, tiles,
-               (__nv_bfloat16*)out, nq, nkv, hd, vd, window, keep_first, sinks, scale);
+               (__nv_bfloat16*)out, nq, nkv, hd, vd, window, keep_first, run, sinks, scale);
   return check_launch("sink_attention_tiles");
 }
 

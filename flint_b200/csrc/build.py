@@ -31,7 +31,7 @@ from ..errors import KernelError
 
 SRC_DIR = Path(__file__).resolve().parent
 MODULES = ("elementwise", "row_fused", "gemm_simt", "gemm_tc", "attention", "attention_tc", "attention_sink", "latent",
-           "mlstm", "moe", "sampling", "noalloc")
+           "mlstm", "recurrent", "moe", "sampling", "noalloc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 HOST_MODULES = ("runtime",)

@@ -476,7 +476,7 @@ extern "C" int flint_gated_act(const float* partials, int S, long long stride, v
 // out[r, c] = act(scale_r * sum_z p[z][r, c]): the epilogue of an ungated product whose K range was split.  Without a
 // list every row has scale 1; with one, assignment a = (token, choice) names the row row_of[a] and its scale
 // row_scale[(a / top) * scale_stride + a % top] (a row no assignment names is left untouched).
-// act: 0 none, 1 gelu (erf), 2 gelu (tanh), 3 silu.
+// act: 0 none, 1 gelu (erf), 2 gelu (tanh), 3 silu, 4 the square of max(x, 0).
 template <typename TO>
 __global__ void row_act_kernel(const float* __restrict__ p, int S, long long stride, TO* __restrict__ out, int rows,
                                int N, int act, const int* __restrict__ row_of, const float* __restrict__ row_scale,
@@ -495,6 +495,7 @@ __global__ void row_act_kernel(const float* __restrict__ p, int S, long long str
     if (act == 1) y = 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
     else if (act == 2) y = 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
     else if (act == 3) y = x / (1.0f + expf(-x));
+    else if (act == 4) y = x > 0.f ? x * x : 0.f;
     out[(size_t)r * N + c] = from_f32<TO>(y);
   }
 }
@@ -504,7 +505,7 @@ extern "C" int flint_row_act(const float* partials, int S, long long stride, voi
                              cudaStream_t stream) {
   if (rows <= 0 || N <= 0) return 0;
   if (S < 1) return fail("row_act: needs at least one partial");
-  if (act < 0 || act > 3) return fail("row_act: unknown activation %d", act);
+  if (act < 0 || act > 4) return fail("row_act: unknown activation %d", act);
   if (row_of && (!row_scale || top < 1 || scale_stride < top)) return fail("row_act: a row list needs scales");
   FLINT_DISPATCH_DTYPE(out_dtype, TO,
       launch_pdl(row_act_kernel<TO>, dim3((unsigned)rows), dim3(N >= 1024 ? 256 : 128), 0, stream, partials, S, stride,

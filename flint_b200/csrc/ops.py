@@ -394,7 +394,7 @@ class CudaOps:
                              c_float(act_params[1]))
         self._gemm(x, w13, True, out, None, False, act, plan)
 
-    ROW_ACTS = {"none": 0, "gelu": 1, "gelu_pytorch_tanh": 2, "silu": 3}
+    ROW_ACTS = {"none": 0, "gelu": 1, "gelu_pytorch_tanh": 2, "silu": 3, "relu2": 4}
 
     def row_act(self, partials, out, act, row_of=None, row_scale=None):
         """out[r] = act(scale_r * sum_z partials[z][r]): partials [S, rows, N] float32 (an ungated product left as
@@ -794,17 +794,20 @@ class CudaOps:
         return keys, -(-span // keys)
 
     def sink_attention(self, q, cache, step, out, nq, nkv, hd, vd, window, keep_first, sinks, scale, splits=None,
-                       tiling=None, rows=None):
+                       tiling=None, rows=None, chunk=0):
         """Every row over its request's cached keys [.., hd] and values [.., vd]: row at position p sees key j if
         j <= p and (p - j < window or j < keep_first) (window 0: all); ``sinks`` [nq] float32 (or None): a logit
         per query head that joins the softmax's denominator.  q [T, nq hd] -> out [T, nq vd].  ``tiling``: the step's
         rows cut into tiles of up to 64 rows (``engine.step.Tiling``): in bfloat16, with head sizes in multiples of
         16 up to 128, the tiles run on the tensor cores and only the rows in no tile row by row.  ``rows``: int32
-        list of the batch rows to compute (default: all)."""
+        list of the batch rows to compute (default: all).  ``chunk`` c > 0 (instead of a window): the row sees key j
+        if j <= p and floor(j / c) = floor(p / c)."""
         _check(q, "q", dims=2)
         _check(out, "out", q.dtype, 2)
         T = q.shape[0]
         P = cache.page_size
+        if chunk and (window or keep_first):
+            raise KernelError("sink_attention: runs of a fixed length exclude a window and kept first tokens")
         if q.shape[1] != nq * hd or tuple(out.shape) != (T, nq * vd):
             raise KernelError("sink_attention: q/out width does not match the head counts")
         if tuple(cache.k.shape[1:]) != (nkv, P, hd) or tuple(cache.v.shape[1:]) != (nkv, P, vd):
@@ -819,7 +822,7 @@ class CudaOps:
             self._run("attention_sink", "flint_sink_attention_tiles", _ptr(q), _ptr(cache.k), _ptr(cache.v),
                       _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(P), _ptr(tiling.tiles),
                       c_int(tiling.n_tiles), _ptr(out), c_int(nq), c_int(nkv), c_int(hd), c_int(vd), c_int(window),
-                      c_int(keep_first), _ptr(sinks), c_float(scale))
+                      c_int(keep_first), c_int(chunk), _ptr(sinks), c_float(scale))
             if not tiling.n_other_rows:
                 return
             rows = tiling.other_rows
@@ -827,6 +830,8 @@ class CudaOps:
             _check(rows, "rows", torch.int32, 1)
             T = rows.numel()
         span = min(step.max_kv_len, window + keep_first) if window else step.max_kv_len
+        if chunk:
+            span = min(span, chunk)
         keys, n = splits if splits is not None else self.sink_attention_plan(T, nq, nkv, span)
         if keys * n < span:
             raise KernelError(f"sink_attention: {n} splits of {keys} keys do not cover {span} keys")
@@ -834,8 +839,8 @@ class CudaOps:
         self._run("attention_sink", "flint_sink_attention", _ptr(q), c_int(_code(q.dtype)), _ptr(cache.k), _ptr(cache.v),
                   c_int(_code(cache.k.dtype)), _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(P),
                   _ptr(step.pos), _ptr(step.slot), _ptr(out), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(vd),
-                  c_int(window), c_int(keep_first), _ptr(sinks), c_float(scale), c_int(keys), c_int(n), _ptr(scratch),
-                  _ptr(rows))
+                  c_int(window), c_int(keep_first), c_int(chunk), _ptr(sinks), c_float(scale), c_int(keys), c_int(n),
+                  _ptr(scratch), _ptr(rows))
 
     @staticmethod
     def sink_attention_tiles_ok(q_dtype, cache_dtype, hd, vd):
@@ -890,6 +895,230 @@ class CudaOps:
             raise KernelError("mlstm_finish: shapes do not match")
         self._run("mlstm", "flint_mlstm_finish", _ptr(o), _ptr(gate), c_longlong(gate.stride(0)), _ptr(norm_w), c_float(eps),
                   _ptr(out), c_int(_code(out.dtype)), c_int(T), c_int(H), c_int(V))
+
+    # ------------------------------------------------------------------ state carried from token to token
+    def short_conv(self, u, col0, w, bias, act, pos, slot, state, y):
+        """y[t, c] = act(bias[c] + sum_j w[c, j] u[t - taps + 1 + j, col0 + c]) over the rows of each request, zeros
+        before its start: u [T, >= col0 + C] float32 rows (a view; rows may be strided), w [C, taps], y [T, C] float32.
+        ``state`` [slots, >= (taps - 1) C] float32 (a view of the slab's rows) holds each request's last taps - 1
+        inputs and is brought up to date.  act: "none" or "silu"."""
+        _check(u, "u", torch.float32, 2, contiguous=False)
+        _check(w, "w", torch.float32, 2)
+        _check(y, "y", torch.float32, 2)
+        C, taps = w.shape
+        T = u.shape[0]
+        if u.stride(1) != 1 or u.shape[1] < col0 + C or tuple(y.shape) != (T, C):
+            raise KernelError("short_conv: shapes do not match")
+        if bias is not None and (bias.dtype != torch.float32 or bias.numel() != C):
+            raise KernelError("short_conv: bias must be float32, one per channel")
+        if act not in ("none", "silu"):
+            raise KernelError(f"short_conv: unknown activation {act!r}")
+        if taps > 1:
+            if state is None:
+                raise KernelError("short_conv: a convolution over time needs the requests' state")
+            _check(state, "state", torch.float32, 2, contiguous=False)
+            if state.stride(1) != 1 or state.shape[1] < (taps - 1) * C:
+                raise KernelError("short_conv: the state's rows are too short")
+        self._run("recurrent", "flint_short_conv", _ptr(u), c_longlong(u.stride(0)), c_int(col0), _ptr(w), _ptr(bias),
+                  c_int(1 if act == "silu" else 0), _ptr(pos), _ptr(slot), _ptr(state),
+                  c_longlong(state.stride(0) if state is not None else 0), _ptr(y), c_int(T), c_int(C), c_int(taps))
+        self.launches += 1 if taps > 1 else 0
+
+    def delta_prepare(self, y, b, a, dt_bias, a_log, qk, decay, beta, H, G, D, unit_eps):
+        """Operands of the gated delta rule from y [T, 2 G D + H V] (q | k | v after their convolution): qk [T, 2 G D]
+        = q and k as unit vectors per head (x / sqrt(sum x^2 + unit_eps); q also times D^(-1/2)); beta [T, H] =
+        sigmoid(b) (b a [T, H] view); decay [T, H D] = exp(-exp(a_log[h]) softplus(a + dt_bias))."""
+        _check(y, "y", torch.float32, 2)
+        _check(b, "b", torch.float32, 2, contiguous=False)
+        for name, t in (("a", a), ("qk", qk), ("decay", decay), ("beta", beta)):
+            _check(t, name, torch.float32, 2)
+        T = y.shape[0]
+        if y.shape[1] < 2 * G * D or tuple(b.shape) != (T, H) or b.stride(1) != 1 or tuple(a.shape) != (T, H * D) \
+                or tuple(qk.shape) != (T, 2 * G * D) or tuple(decay.shape) != (T, H * D) or tuple(beta.shape) != (T, H) \
+                or dt_bias.numel() != H * D or a_log.numel() != H:
+            raise KernelError("delta_prepare: shapes do not match")
+        self._run("recurrent", "flint_delta_prepare", _ptr(y), c_longlong(y.stride(0)), _ptr(b), c_longlong(b.stride(0)),
+                  _ptr(a), _ptr(dt_bias), _ptr(a_log), _ptr(qk), _ptr(decay), _ptr(beta), c_int(T), c_int(H), c_int(G),
+                  c_int(D), c_float(unit_eps))
+
+    def ssd_prepare(self, raw, dt_bias, a_log, dt, decay):
+        """dt = softplus(raw + dt_bias), decay = exp(-exp(a_log) dt): raw a [T, H] float32 view, dt and decay [T, H]."""
+        _check(raw, "raw", torch.float32, 2, contiguous=False)
+        _check(dt, "dt", torch.float32, 2)
+        _check(decay, "decay", torch.float32, 2)
+        T, H = raw.shape
+        if raw.stride(1) != 1 or tuple(dt.shape) != (T, H) or tuple(decay.shape) != (T, H) or dt_bias.numel() != H \
+                or a_log.numel() != H:
+            raise KernelError("ssd_prepare: shapes do not match")
+        self._run("recurrent", "flint_ssd_prepare", _ptr(raw), c_longlong(raw.stride(0)), _ptr(dt_bias), _ptr(a_log), _ptr(dt),
+                  _ptr(decay), c_int(T), c_int(H))
+
+    def recurrence_scan(self, q, k, v, decay, delta, beta, dt, skip, slot, seq_start, n_seq, state, out, H, G, D, V):
+        """Walks every request's rows in order (request e owns rows seq_start[e] .. seq_start[e + 1] - 1;
+        ``seq_start`` None: row e alone) from and into ``state`` [slots, >= H D V] float32, per head a matrix S [D, V]:
+        ``delta``: S <- diag(decay_t) S; u = beta_t (v_t - S^T k_t); S <- S + k_t u^T; o_t = S^T q_t (decay [T, H D]);
+        else:      S <- decay_t S + k_t (dt_t v_t)^T; o_t = S^T q_t + skip v_t (decay, dt [T, H]; skip [H] or None).
+        q, k [T, G D] and v [T, H V] are float32 views (rows may be strided); out [T, H V] float32."""
+        for name, t in (("q", q), ("k", k), ("v", v)):
+            _check(t, name, torch.float32, 2, contiguous=False)
+            if t.stride(1) != 1:
+                raise KernelError(f"recurrence_scan: {name}'s rows must be dense")
+        w1 = beta if delta else dt
+        for name, t in (("decay", decay), ("beta" if delta else "dt", w1), ("out", out)):
+            _check(t, name, torch.float32, 2)
+        _check(state, "state", torch.float32, 2, contiguous=False)
+        T = q.shape[0]
+        if tuple(q.shape) != (T, G * D) or tuple(k.shape) != (T, G * D) or tuple(v.shape) != (T, H * V) \
+                or tuple(decay.shape) != (T, H * D if delta else H) or tuple(w1.shape) != (T, H) \
+                or tuple(out.shape) != (T, H * V) or state.stride(1) != 1 or state.shape[1] < H * D * V:
+            raise KernelError("recurrence_scan: shapes do not match")
+        if skip is not None and (skip.dtype != torch.float32 or skip.numel() != H):
+            raise KernelError("recurrence_scan: skip must be float32, one per head")
+        if seq_start is not None:
+            _check(seq_start, "seq_start", torch.int32, 1)
+            if seq_start.numel() != n_seq + 1:
+                raise KernelError("recurrence_scan: seq_start must have one entry more than there are requests")
+        elif n_seq != T:
+            raise KernelError("recurrence_scan: without seq_start every request brings one row")
+        self._run("recurrent", "flint_recurrence_scan", _ptr(q), c_longlong(q.stride(0)), _ptr(k), c_longlong(k.stride(0)),
+                  _ptr(v), c_longlong(v.stride(0)), _ptr(decay), c_int(1 if delta else 0), _ptr(w1), _ptr(skip), _ptr(slot),
+                  _ptr(seq_start), c_int(n_seq), _ptr(state), c_longlong(state.stride(0)), _ptr(out), c_int(H), c_int(G),
+                  c_int(D), c_int(V))
+
+    def gated_norm(self, o, gate, gate_act, gate_first, w, eps, groups, out):
+        """o [T, N] float32 in ``groups`` equal parts, each divided by its own root mean square (eps inside the
+        root), times w (its numbers repeat over the row: one per dim of a head, or one per channel) and times
+        act(gate) (a [T, N] float32 view; "sigmoid" or "silu"); ``gate_first``: the gate multiplies before the norm."""
+        _check(o, "o", torch.float32, 2)
+        _check(gate, "gate", torch.float32, 2, contiguous=False)
+        _check(w, "w", torch.float32, 1)
+        _check(out, "out", dims=2)
+        T, N = o.shape
+        if tuple(gate.shape) != (T, N) or gate.stride(1) != 1 or tuple(out.shape) != (T, N) or N % groups \
+                or N % w.numel():
+            raise KernelError("gated_norm: shapes do not match")
+        if gate_act not in ("sigmoid", "silu"):
+            raise KernelError(f"gated_norm: unknown gate {gate_act!r}")
+        self._run("recurrent", "flint_gated_norm", _ptr(o), _ptr(gate), c_longlong(gate.stride(0)),
+                  c_int(1 if gate_act == "silu" else 0), c_int(1 if gate_first else 0), _ptr(w), c_int(w.numel()), c_float(eps),
+                  c_int(groups), c_int(N), _ptr(out), c_int(_code(out.dtype)), c_int(T))
+
+    def branch_mean(self, branches, weights, eps, out):
+        """out[t] = (1 / n) sum_b weights[b] * y_b[t] / sqrt(mean(y_b[t]^2) + eps), y_b the sum of branch b's partial
+        sums plus its bias: ``branches`` [(partials [S, T, W] float32, bias [W] or None)], out [T, W] float32."""
+        n = len(branches)
+        if not 1 <= n <= 4 or len(weights) != n:
+            raise KernelError("branch_mean: one to four branches, a weight each")
+        _check(out, "out", torch.float32, 2)
+        T, W = out.shape
+        ptrs, strides, counts, biases, ws = [], [], [], [], []
+        for (part, bias), w in zip(branches, weights):
+            _check(part, "partials", torch.float32, 3)
+            if tuple(part.shape[1:]) != (T, W) or w.dtype != torch.float32 or w.numel() != W:
+                raise KernelError("branch_mean: shapes do not match")
+            if bias is not None and (bias.dtype != torch.float32 or bias.numel() != W):
+                raise KernelError("branch_mean: a bias must be float32 of the rows' width")
+            ptrs.append(part.data_ptr())
+            strides.append(part.stride(0))
+            counts.append(part.shape[0])
+            biases.append(bias.data_ptr() if bias is not None else 0)
+            ws.append(w.data_ptr())
+        arr = lambda ctype, vals: (ctype * n)(*vals)
+        self._run("recurrent", "flint_branch_mean", c_int(n), arr(c_void_p, ptrs), arr(c_longlong, strides), arr(c_int, counts),
+                  arr(c_void_p, biases), arr(c_void_p, ws), c_float(eps), _ptr(out), c_int(T), c_int(W))
+
+    def post_norm(self, x, partials, bias, scale, residual_scale, gamma, beta, eps, mode, out_copy=None):
+        """x <- norm(residual_scale x + scale * (sum of partials + bias)) in place: x [T, W] float32, partials
+        [S, T, W] float32, scale [W] or None; ``mode`` "layer" or "rms"; ``out_copy`` [T, W] of another
+        element type receives the result too."""
+        _check(x, "x", torch.float32, 2)
+        _check(partials, "partials", torch.float32, 3)
+        T, W = x.shape
+        if tuple(partials.shape[1:]) != (T, W) or gamma.numel() != W or gamma.dtype != torch.float32:
+            raise KernelError("post_norm: shapes do not match")
+        for name, t in (("bias", bias), ("scale", scale), ("beta", beta)):
+            if t is not None and (t.dtype != torch.float32 or t.numel() != W):
+                raise KernelError(f"post_norm: {name} must be float32 of the rows' width")
+        if out_copy is not None:
+            _check(out_copy, "out_copy", dims=2)
+            if tuple(out_copy.shape) != (T, W):
+                raise KernelError("post_norm: the copy must have the rows' shape")
+        self._run("recurrent", "flint_post_norm", _ptr(x), _ptr(partials), c_int(partials.shape[0]),
+                  c_longlong(partials.stride(0)), _ptr(bias), _ptr(scale), c_float(residual_scale), _ptr(gamma), _ptr(beta),
+                  c_float(eps), c_int({"layer": 0, "rms": 1}[mode]), _ptr(out_copy),
+                  c_int(_code(out_copy.dtype) if out_copy is not None else F32), c_int(T), c_int(W))
+
+    def depth_mix(self, history, n, w, h, out_copy=None):
+        """history[n - 1] <- h, then h <- sum over j < n of w[j] history[j]: history [levels, T, W] float32, w [>= n]
+        float32, h [T, W] float32; ``out_copy`` receives the new h in another element type too."""
+        _check(history, "history", torch.float32, 3)
+        _check(h, "h", torch.float32, 2)
+        if n < 1 or n > history.shape[0] or tuple(history.shape[1:]) != tuple(h.shape) or w.numel() < n \
+                or w.dtype != torch.float32:
+            raise KernelError("depth_mix: shapes do not match")
+        if out_copy is not None:
+            _check(out_copy, "out_copy", dims=2)
+        self._run("recurrent", "flint_depth_mix", _ptr(history), c_longlong(history.stride(0)), c_int(n), _ptr(w), _ptr(h),
+                  _ptr(out_copy), c_int(_code(out_copy.dtype) if out_copy is not None else F32), c_longlong(h.numel()))
+
+    def softcap(self, x, cap):
+        """x <- cap tanh(x / cap) in place (float32)."""
+        _check(x, "x", torch.float32)
+        self._run("recurrent", "flint_softcap", _ptr(x), c_float(cap), c_longlong(x.numel()))
+
+    def cast_rows(self, x, out):
+        """out <- x in out's element type (x float32, same shape)."""
+        _check(x, "x", torch.float32)
+        _check(out, "out")
+        if out.shape != x.shape:
+            raise KernelError("cast_rows: shapes differ")
+        self._run("recurrent", "flint_cast_rows", _ptr(x), _ptr(out), c_int(_code(out.dtype)), c_longlong(x.numel()))
+
+    def qk_norm_write(self, y, q_norm, k_norm, eps, pos, slot, cos, sin, rot, style, v_cos, v_sin, v_style, q_out, cache,
+                      nq, nkv, hd, vd, status):
+        """y [T, (nq + nkv) hd + nkv vd] float32 (q | k | v): every q and k head is divided by its root mean square
+        and scaled by q_norm / k_norm [hd] (both None: no norm), its leading ``rot`` dims rotate by the row's
+        position; every value head rotates over all vd dims with tables of its own (None: not at all).  q goes to
+        q_out [T, nq hd], keys and values into the row's cache page."""
+        _check(y, "y", torch.float32, 2, contiguous=False)
+        T = y.shape[0]
+        if y.stride(1) != 1 or y.shape[1] < (nq + nkv) * hd + nkv * vd:
+            raise KernelError("qk_norm_write: the rows' width does not match the head counts")
+        _check(q_out, "q_out", dims=2)
+        if tuple(q_out.shape) != (T, nq * hd):
+            raise KernelError(f"qk_norm_write: q_out must be [{T}, {nq * hd}]")
+        for name, t, n in (("q_norm", q_norm, hd), ("k_norm", k_norm, hd)):
+            if t is not None and (t.dtype != torch.float32 or t.numel() != n):
+                raise KernelError(f"qk_norm_write: {name} must be float32 [{n}]")
+        if rot and (cos is None or cos.shape[1] * 2 != rot):
+            raise KernelError("qk_norm_write: table width must be rot/2")
+        if v_cos is not None and v_cos.shape[1] * 2 != vd:
+            raise KernelError("qk_norm_write: the values' table width must be vd/2")
+        k, v, bt, P = cache.k, cache.v, cache.block_table, cache.page_size
+        if tuple(k.shape[1:]) != (nkv, P, hd) or tuple(v.shape[1:]) != (nkv, P, vd) or v.dtype != k.dtype:
+            raise KernelError(f"qk_norm_write: cache pages are {tuple(k.shape[1:])} and {tuple(v.shape[1:])}, expected "
+                              f"{(nkv, P, hd)} and {(nkv, P, vd)}")
+        self._run("recurrent", "flint_qk_norm_write", _ptr(y), c_longlong(y.stride(0)), _ptr(q_norm), _ptr(k_norm), c_float(eps),
+                  _ptr(pos), _ptr(slot), _ptr(cos), _ptr(sin), c_int(rot), c_int(1 if style == "interleaved" else 0),
+                  _ptr(v_cos), _ptr(v_sin), c_int(1 if v_style == "interleaved" else 0), _ptr(q_out),
+                  c_int(_code(q_out.dtype)), _ptr(k), _ptr(v), c_int(_code(k.dtype)), _ptr(bt), c_int(bt.shape[1]), c_int(P),
+                  c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(vd), _ptr(status))
+
+    def head_finish(self, attn, pos, v_cos, v_sin, v_style, gate, out, nq, vd):
+        """attn [T, nq vd]: every head's sum is turned back by the row's position (tables None: not at all) and
+        multiplied by sigmoid(gate[t, head]) (gate a [T, nq] float32 view, or None)."""
+        _check(attn, "attn", dims=2)
+        _check(out, "out", attn.dtype, 2)
+        T = attn.shape[0]
+        if tuple(attn.shape) != (T, nq * vd) or out.shape != attn.shape:
+            raise KernelError("head_finish: shapes do not match")
+        if gate is not None:
+            _check(gate, "gate", torch.float32, 2, contiguous=False)
+            if tuple(gate.shape) != (T, nq) or gate.stride(1) != 1:
+                raise KernelError("head_finish: the gates must be [rows, heads]")
+        self._run("recurrent", "flint_head_finish", _ptr(attn), c_int(_code(attn.dtype)), _ptr(pos), _ptr(v_cos), _ptr(v_sin),
+                  c_int(1 if v_style == "interleaved" else 0), _ptr(gate),
+                  c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out), c_int(T), c_int(nq), c_int(vd))
 
     # ------------------------------------------------------------------ attention over a cached latent
     def head_products(self, x, w, out):

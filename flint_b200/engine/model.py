@@ -40,6 +40,7 @@ def registry_for_role(role: str):
 class Layer:
     def __init__(self, spec, ctx):
         self.spec = spec
+        self.ctx = ctx
         self.parts = {role: registry_for_role(role).get(ps.kind)(ps.params, ctx) for role, ps in spec.parts.items()}
         self.block = BLOCKS.get(spec.block)(self.parts)
         missing = [r for r in self.block.roles if r not in self.parts]
@@ -72,9 +73,30 @@ def build_embed_additions(spec: ModelSpec, ctx) -> list:
     return [(EMBED_ADDITIONS.get(ps.kind)(ps.params, ctx), prefix) for ps, prefix in spec.embed_additions]
 
 
+def embed_norm_of(spec: ModelSpec, ctx):
+    """The norm of the embedded rows that ``spec`` names, or None."""
+    return NORMS.get(spec.embed_norm.kind)(spec.embed_norm.params, ctx) if spec.embed_norm is not None else None
+
+
+def depth_mix_names(spec: ModelSpec) -> list:
+    """The tensor of every call of the run order that holds its weights over the rows so far ([] without depth mix)."""
+    if not spec.depth_mix:
+        return []
+    return [spec.layers[call.layer].prefix + spec.depth_mix_name for call in spec.order]
+
+
 def expected_tensors(spec: ModelSpec, layers, final_norm, embed_position=None, embed_additions=()) -> dict:
     """Every tensor name the model reads, with its shape and role."""
     exp = {spec.embed_name + "weight": WeightSpec((spec.vocab_size, spec.hidden_size))}
+    if spec.embed_norm is not None:
+        ctx = layers[0].ctx if layers else None
+        for name, ws in embed_norm_of(spec, ctx).weights().items():
+            exp[spec.embed_norm_name + name] = ws
+    names = depth_mix_names(spec)
+    if len(set(names)) != len(names):
+        raise ConfigError("depth mix: a layer that is called twice cannot store one set of weights per call")
+    for i, name in enumerate(names):
+        exp[name] = WeightSpec((i + 2,), role="vector", init="gamma")
     if embed_position is not None:
         for name, ws in embed_position.weights().items():
             exp[spec.embed_position_name + name] = ws
@@ -136,6 +158,10 @@ class Model:
         self.head_weight = self.embed_table if spec.tie_word_embeddings else tensors[spec.head_name + "weight"]
         self.head_bias = tensors.get(spec.head_name + "bias")
         self.final_norm.load({n: tensors[spec.final_norm_name + n] for n in self.final_norm.weights()})
+        self.embed_norm = embed_norm_of(spec, self.ctx)
+        if self.embed_norm is not None:
+            self.embed_norm.load({n: tensors[spec.embed_norm_name + n] for n in self.embed_norm.weights()})
+        self.depth_weights = [tensors[n] for n in depth_mix_names(spec)]
         if self.embed_position is not None:
             self.embed_position.load({n: tensors[spec.embed_position_name + n] for n in self.embed_position.weights()})
         for part, prefix in self.embed_additions:
@@ -185,6 +211,7 @@ class Model:
         # decode steps (one token per entry) are captured once per batch size and mixers' plan (the attention's
         # key-range split), and replayed: their hundreds of small launches would otherwise be bound by the host
         self.use_graphs = (use_graphs and self.device.type == "cuda" and self.final_norm.graph_safe
+                           and (self.embed_norm is None or self.embed_norm.graph_safe)
                            and (self.embed_position is None or self.embed_position.graph_safe)
                            and all(part.graph_safe for part, _ in self.embed_additions)
                            and all(p.graph_safe for layer in self.layers for p in layer.parts.values()))
@@ -288,18 +315,45 @@ class Model:
             self.embed_position.after_embedding(h, step)
         for k, (part, _) in enumerate(self.embed_additions):
             part.forward(h, step, self.cache.state_of(("embed", k)), fed_from=self.fed_from)
+        # a copy of the rows in the activations' type, for parts that read the rows themselves (no norm before them)
+        copy = (torch.empty((T, spec.hidden_size), dtype=self.ctx.act_dtype, device=self.device)
+                if self.ctx.act_dtype != torch.float32 and (self.embed_norm is not None or spec.depth_mix) else None)
+        history = None
+        if spec.depth_mix:       # the embedded rows and every call's result: what a call hands on is a weighted sum of them
+            history = torch.empty((len(self.order) + 1, T, spec.hidden_size), dtype=torch.float32, device=self.device)
+        if self.embed_norm is not None:
+            normed = history[0] if history is not None else torch.empty_like(h)
+            self.embed_norm.forward(h, (), out={torch.float32: normed, **({copy.dtype: copy} if copy is not None else {})})
+            if history is not None:
+                h.copy_(normed)
+            else:
+                h = normed
+            if copy is not None:
+                step.shared["rows"] = (h, {copy.dtype: copy})
+        elif history is not None:
+            history[0].copy_(h)
         carry = None     # an addition to h that a layer left for the next norm to apply
         for i, call in enumerate(self.order):
             layer = self.layers[call.layer]
             owner = i if call.cache_of is None else call.cache_of
             carry = layer.block.forward(h, step, self.cache.view(owner), self.cache.state_of(i),
                                         writes_cache=call.cache_of is None, carry=carry)
+            if history is not None:
+                if carry is not None:
+                    ops.apply_pending(h, carry)
+                    carry = None
+                # history[i + 1] <- h, then h <- sum_j w[j] history[j] over the i + 2 sets of rows so far
+                ops.depth_mix(history, i + 2, self.depth_weights[i], h, out_copy=copy)
+                if copy is not None:
+                    step.shared["rows"] = (h, {copy.dtype: copy})
         R = step.n_want
         logits = torch.empty((R, spec.vocab_size), dtype=torch.float32, device=self.device)
         if R:
             wdt = self.head_weight.dtype
             x, _ = run_norm(self.final_norm, h, (wdt,), carry, row_index=step.want_rows)
             ops.gemm(x[wdt], self.head_weight, logits, bias=self.head_bias)
+            if spec.logit_softcap:
+                ops.softcap(logits, spec.logit_softcap)
         return logits
 
     def check_status(self, flags=None):

@@ -13,7 +13,7 @@ import math
 
 import torch
 
-from ..cache.manager import KVSpec
+from ..cache.manager import KVSpec, StateSpec
 from ..engine.step import StepNeeds
 from ..errors import ConfigError, ModelError
 from ..registry import MIXERS, POSITION_ENCODINGS
@@ -39,10 +39,21 @@ class Attention(Mixer):
     query head, tensor ``sinks`` [num_heads], that joins the softmax's denominator without a key or a value),
     value_mix ("source": this layer's values, as projected, are left for later layers of the step; "blend":
     v <- (1 - a) v + a v_source with the scalar tensor ``value_mix`` = a, before v is cached; the tensor may be
-    stored for a source too, which ignores it).  A layer that uses any of these runs on the general attention
-    kernels (``csrc/attention_sink.cu``)."""
+    stored for a source too, which ignores it), chunk (c > 0: the sequence is cut into runs of c positions counted
+    from position 0, and a position sees only the earlier positions of its own run).  A layer that uses any of
+    these runs on the general attention kernels (``csrc/attention_sink.cu``).
+
+    And what happens around the attention itself: conv_taps (n >= 1: q, k and v pass a causal convolution of n taps
+    per channel right after the projection, tensors ``q_conv.weight`` / ``k_conv.weight`` / ``v_conv.weight``
+    [channels, n]; the last n - 1 projected rows of a request are fixed-size state), qk_norm (q and k are divided by
+    their root mean square per head, eps ``qk_norm_eps``, and scaled by ``q_norm.weight`` / ``k_norm.weight``
+    [head_dim], before they rotate), value_position (a PartSpec of a rotary encoding over all value dims: the
+    value of position j is cached turned by j, and every head's sum is turned back by its query's position),
+    head_gate (every head's output times sigmoid(W x), one number a head, tensor ``gate_proj.weight`` [num_heads,
+    hidden])."""
 
     graph_safe = True
+    returns_pending = True       # the output projection always leaves as partial sums; the rows given are not touched
     # portions of at least 16 rows go to the tensor-core attention in tiles of 128 query rows, the rest row by row
     NEEDS = StepNeeds(tile_rows=128, tile_min_rows=16)
     # the general kernels' tensor-core form takes tiles of 64 rows
@@ -62,7 +73,24 @@ class Attention(Mixer):
         self.value_mix = p.get("value_mix")
         if self.value_mix not in (None, "source", "blend"):
             raise ConfigError(f"value_mix must be 'source' or 'blend', got {self.value_mix!r}")
-        self.general = bool(self.vd != self.hd or self.keep_first or self.sinks or self.value_mix)
+        self.chunk = int(p.get("chunk", 0) or 0)
+        if self.chunk and self.window:
+            raise ConfigError("attention: a window and runs of a fixed length cannot be combined")
+        self.taps = int(p.get("conv_taps", 0) or 0)
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.qk_eps = float(p.get("qk_norm_eps", 1e-6))
+        self.head_gate = bool(p.get("head_gate", False))
+        self.value_position = (shared_position_encoding(p["value_position"], ctx)
+                               if p.get("value_position") is not None else None)
+        if self.value_position is not None and self.value_position.rotary_dim != self.vd:
+            raise ConfigError("attention: the values' rotation must cover all value dims")
+        # q, k and v take a longer way from the projection to the cache, and the heads' sums one to the output
+        self.reworked = bool(self.taps or self.qk_norm or self.head_gate or self.value_position is not None)
+        if self.reworked and self.value_mix:
+            raise ConfigError("attention: blended values cannot be combined with a convolution, q/k norms, rotated "
+                              "values or a gate per head")
+        self.general = bool(self.vd != self.hd or self.keep_first or self.sinks or self.value_mix or self.chunk
+                            or self.reworked)
         if self.general:
             if max(self.hd, self.vd) > 256 or min(self.hd, self.vd) < 1:
                 raise ConfigError(f"head sizes {self.hd} (keys) and {self.vd} (values) are not supported (1 to 256)")
@@ -89,6 +117,13 @@ class Attention(Mixer):
             w["sinks"] = vec(nq)
         if "value_mix" in self.params:
             w["value_mix"] = WeightSpec((), role="vector", optional=self.value_mix != "blend")
+        if self.taps:
+            for n, rows in (("q", nq * hd), ("k", nkv * hd), ("v", nkv * vd)):
+                w[f"{n}_conv.weight"] = WeightSpec((rows, self.taps), role="vector", std=0.3)
+        if self.qk_norm:
+            w.update({"q_norm.weight": vec(hd, init="gamma"), "k_norm.weight": vec(hd, init="gamma")})
+        if self.head_gate:
+            w["gate_proj.weight"] = mat(nq, H)
         return w
 
     def fused(self):
@@ -99,9 +134,18 @@ class Attention(Mixer):
 
     def load(self, t):
         dt = matmul_dtype(t["q_proj.weight"], t["k_proj.weight"], t["v_proj.weight"])
-        self.w_qkv = torch.cat([t["q_proj.weight"].to(dt), t["k_proj.weight"].to(dt), t["v_proj.weight"].to(dt)], 0)
+        # one product gives q, k, v and, with a gate per head, its logits
+        pieces = [t["q_proj.weight"], t["k_proj.weight"], t["v_proj.weight"]] + ([t["gate_proj.weight"]] if self.head_gate else [])
+        self.w_qkv = torch.cat([w.to(dt) for w in pieces], 0)
+        self.w_conv = (torch.cat([t["q_conv.weight"], t["k_conv.weight"], t["v_conv.weight"]], 0).contiguous()
+                       if self.taps else None)
+        self.q_norm, self.k_norm = t.get("q_norm.weight"), t.get("k_norm.weight")
+        self.v_cos, self.v_sin = self.value_position.tables() if self.value_position is not None else (None, None)
         self.b_qkv = (torch.cat([t["q_proj.bias"], t["k_proj.bias"], t["v_proj.bias"]], 0).contiguous()
                       if self.qkv_bias else None)
+        # the same for a projection that also gives the gates' logits (which have no bias)
+        self.b_qkv_all = (torch.cat([self.b_qkv, self.b_qkv.new_zeros(self.nq)]) if self.qkv_bias and self.head_gate
+                          else self.b_qkv)
         self.w_o = t["o_proj.weight"]
         self.b_o = t.get("o_proj.bias")
         self.sink = t.get("sinks")
@@ -120,6 +164,11 @@ class Attention(Mixer):
             return KVSpec(self.nkv, self.hd, self.window, value_dim=None if self.vd == self.hd else self.vd,
                           keep_first=self.keep_first)
         return KVSpec(self.nkv, self.hd, self.window)
+
+    def state_spec(self):
+        if self.taps > 1:        # the last taps - 1 projected rows of q | k | v
+            return StateSpec(((self.taps - 1) * ((self.nq + self.nkv) * self.hd + self.nkv * self.vd),), torch.float32)
+        return None
 
     def step_needs(self):
         if not self.general:
@@ -156,12 +205,50 @@ class Attention(Mixer):
         step.max_kv_len = -(-kv // gran) * gran
         return (step.max_kv_len,)
 
-    def _forward_general(self, xin, step, cache, writes_cache):
+    def _forward_reworked(self, xin, step, cache, state):
+        """The general kernels with more on both sides: the projection (with the gates' logits), the convolution over
+        each request's rows and its carried ones, one kernel that norms and rotates q and k, rotates the values and
+        writes q and the cache rows, the attention, one kernel that turns every head's sum back and gates it, and
+        the output projection as partial sums."""
+        ops, nq, nkv, hd, vd = self.ops, self.nq, self.nkv, self.hd, self.vd
+        T, dev = xin.shape[0], xin.device
+        act = self.ctx.act_dtype if self.w_qkv.dtype == torch.bfloat16 else torch.float32
+        W = (nq + nkv) * hd + nkv * vd
+        proj = torch.empty((T, self.w_qkv.shape[0]), dtype=torch.float32, device=dev)
+        ops.gemm(xin, self.w_qkv, proj, bias=self.b_qkv_all)
+        if self.taps:
+            if self.taps > 1 and state is None:
+                raise ModelError("attention: the convolution needs a state slab")
+            y = torch.empty((T, W), dtype=torch.float32, device=dev)
+            ops.short_conv(proj, 0, self.w_conv, None, "none", step.pos, step.slot, state, y)
+        else:
+            y = proj[:, :W]
+        q = torch.empty((T, nq * hd), dtype=act, device=dev)
+        ops.qk_norm_write(y, self.q_norm, self.k_norm, self.qk_eps, step.pos, step.slot, self.cos, self.sin, self.rot,
+                          self.rot_style, self.v_cos, self.v_sin,
+                          self.value_position.style if self.value_position is not None else "half", q, cache, nq, nkv, hd,
+                          vd, step.status)
+        attn = torch.empty((T, nq * vd), dtype=act, device=dev)
+        needs = self.step_needs()
+        ops.sink_attention(q, cache, step, attn, nq, nkv, hd, vd, self.window, self.keep_first, self.sink, self.scale,
+                           tiling=step.tiling(needs) if needs is not None and q.dtype == torch.bfloat16 else None,
+                           chunk=self.chunk)
+        if self.head_gate or self.value_position is not None:
+            out = torch.empty_like(attn)
+            ops.head_finish(attn, step.pos, self.v_cos, self.v_sin,
+                            self.value_position.style if self.value_position is not None else "half",
+                            proj[:, W:] if self.head_gate else None, out, nq, vd)
+            attn = out
+        return Pending(partials=ops.gemm_partials(attn, self.w_o), bias=self.b_o)
+
+    def _forward_general(self, xin, step, cache, writes_cache, state=None):
         """Sizes and masks the fast kernels do not take: projection left as partial sums, one kernel that adds
         them with the bias, rotates, blends the values and writes q and the cache rows, one attention kernel
         with the window's kept first tokens and the sink, then the output projection as partial sums."""
         if not writes_cache:
             raise ModelError("attention: a layer on the general kernels owns its cache")
+        if self.reworked:
+            return self._forward_reworked(xin, step, cache, state)
         ops, nq, nkv, hd, vd = self.ops, self.nq, self.nkv, self.hd, self.vd
         T, dev = xin.shape[0], xin.device
         act = self.ctx.act_dtype if self.w_qkv.dtype == torch.bfloat16 else torch.float32
@@ -180,14 +267,15 @@ class Attention(Mixer):
         attn = torch.empty((T, nq * vd), dtype=act, device=dev)
         needs = self.step_needs()
         ops.sink_attention(q, cache, step, attn, nq, nkv, hd, vd, self.window, self.keep_first, self.sink, self.scale,
-                           tiling=step.tiling(needs) if needs is not None and q.dtype == torch.bfloat16 else None)
+                           tiling=step.tiling(needs) if needs is not None and q.dtype == torch.bfloat16 else None,
+                           chunk=self.chunk)
         return Pending(partials=ops.gemm_partials(attn, self.w_o), bias=self.b_o)
 
     def forward(self, x, residual, step, cache, state, writes_cache=True):
         if cache is None:
             raise ModelError("attention needs a cache")
         if self.general:
-            return self._forward_general(x[self.w_qkv.dtype], step, cache, writes_cache)
+            return self._forward_general(x[self.w_qkv.dtype], step, cache, writes_cache, state)
         ops, nq, nkv, hd = self.ops, self.nq, self.nkv, self.hd
         xin = x[self.w_qkv.dtype]
         T = xin.shape[0]

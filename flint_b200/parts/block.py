@@ -4,6 +4,8 @@
 (crates/thuban_architectures/src/transformer/forward.rs:102-440) and Phi-MoE's.
 ``parallel``: h += mixer(norm1(h)) + ffn(norm1(h)) with one shared norm (the feed-forward may be absent);
 ``parallel_two_norms``: h += mixer(norm1(h)) + ffn(norm2(h)), both of the same h.
+``postnorm``: h <- norm1(a h + s1 * mixer(h)); h <- norm2(a h + s2 * ffn(h)): the parts read the rows themselves and
+the norms come after the sums (a and the scales s are the norms' ``residual_scale`` and ``branch_scale``).
 An arrangement only orders parts; it does not know what they are.
 """
 from __future__ import annotations
@@ -129,3 +131,65 @@ class ParallelTwoNormsBlock(Block):
         mixed = mixer.forward(x, residual, step, cache, state, writes_cache)
         fed = ffn.forward(y, residual, step, routed=routed) if routed is not None else ffn.forward(y, residual, step)
         return merge_pending(mixer, residual, mixed, fed)
+
+
+def rows_in(part_ops, residual, step, dtypes):
+    """The rows themselves in the element types a part reads: the float32 rows as they are; another type from the
+    copy that the producer of the rows left in ``step.shared["rows"]`` (tensor, {type: copy}), else cast here."""
+    left = step.shared.get("rows")
+    copies = left[1] if left is not None and left[0] is residual else {}
+    out = {}
+    for dt in set(dtypes):
+        if dt == residual.dtype:
+            out[dt] = residual
+        elif dt in copies:
+            out[dt] = copies[dt]
+        else:
+            out[dt] = torch.empty(residual.shape, dtype=dt, device=residual.device)
+            part_ops.cast_rows(residual, out[dt])
+    return out
+
+
+def branch_of(part, residual, run):
+    """What a part adds, as a ``Pending`` of partial sums that nobody has applied.  A part that says
+    ``returns_pending`` never touches the rows it is given and always returns such a ``Pending``; any other part
+    adds into a zeroed float32 buffer shaped like ``residual``, which then is the one partial sum.  ``run(rows)`` calls
+    the part's forward."""
+    if getattr(part, "returns_pending", False):
+        return run(None)
+    buf = torch.zeros(residual.shape, dtype=torch.float32, device=residual.device)
+    pend = run(buf)
+    if pend is not None:
+        part.ops.apply_pending(buf, pend)
+    return Pending(partials=buf.unsqueeze(0))
+
+
+@BLOCKS.register("postnorm")
+class PostNormBlock(Block):
+    """h <- norm1(a h + s1 * mixer(h)); h <- norm2(a h + s2 * ffn(h)), the second half only with a feed-forward.
+    Both norms must be able to run after the sum (``Norm.post``)."""
+    roles = ("norm1", "mixer")
+
+    def forward(self, residual, step, cache, state, writes_cache=True, carry=None):
+        p = self.parts
+        mixer, ffn = p["mixer"], p.get("ffn")
+        settle(mixer, residual, carry)
+        act = mixer.ctx.act_dtype
+        x = rows_in(mixer.ops, residual, step, mixer.input_dtypes())
+        step.shared.pop("rows", None)          # the rows change below
+        mixed = branch_of(mixer, residual, lambda rows: mixer.forward(x, rows, step, cache, state, writes_cache))
+        if ffn is None:
+            p["norm1"].post(residual, mixed)
+            return None
+        if "norm2" not in p:
+            raise ConfigError("block 'postnorm': a feed-forward needs its norm (norm2)")
+        want = set(ffn.input_dtypes())
+        copy = torch.empty(residual.shape, dtype=act, device=residual.device) if act in want and act != residual.dtype else None
+        p["norm1"].post(residual, mixed, copy=copy)
+        if copy is not None:
+            step.shared["rows"] = (residual, {act: copy})
+        y = rows_in(ffn.ops, residual, step, want)
+        step.shared.pop("rows", None)
+        fed = branch_of(ffn, residual, lambda rows: ffn.forward(y, rows, step))
+        p["norm2"].post(residual, fed)
+        return None

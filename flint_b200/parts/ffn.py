@@ -62,6 +62,39 @@ class GatedMLP(FeedForward):
         self.ops.gemm(a, self.w_down, residual, accumulate=True)
 
 
+@FEED_FORWARDS.register("mlp")
+class PlainMLP(FeedForward):
+    """An ungated unit: act(x Wu^T) Wd^T.  params: hidden_size, intermediate_size, act (``relu2``: the square of
+    max(z, 0); ``gelu``, ``gelu_pytorch_tanh``, ``silu``); tensors up_proj [I,H], down_proj [H,I].  The down
+    product is left as partial sums for whoever applies it."""
+
+    graph_safe = True
+    returns_pending = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        self.act = params.get("act", "gelu")
+        if self.act not in ("relu2", "gelu", "gelu_pytorch_tanh", "silu"):
+            raise ConfigError(f"mlp: unknown activation {self.act!r}")
+
+    def weights(self):
+        return {"up_proj.weight": mat(self.inter, self.hidden), "down_proj.weight": mat(self.hidden, self.inter)}
+
+    def load(self, t):
+        dt = matmul_dtype(*t.values())
+        self.w_up, self.w_down = t["up_proj.weight"].to(dt), t["down_proj.weight"].to(dt)
+
+    def input_dtypes(self):
+        return (self.w_up.dtype,)
+
+    def forward(self, x, residual, step):
+        xin = x[self.w_up.dtype]
+        a = torch.empty((xin.shape[0], self.inter), dtype=self.w_up.dtype, device=xin.device)
+        self.ops.row_act(self.ops.gemm_partials(xin, self.w_up), a, self.act)
+        return Pending(partials=self.ops.gemm_partials(a, self.w_down))
+
+
 @FEED_FORWARDS.register("sparsemixer_moe")
 class SparseMixerMoE(FeedForward):
     """params: hidden_size, intermediate_size, num_experts, jitter_eps, act.

@@ -16,6 +16,12 @@ from .safetensors_io import save_safetensors
 from .sources import FusedView, RandomSource, WeightSpec
 
 
+def same_shape(found: tuple, spec: WeightSpec) -> bool:
+    """Whether a stored shape is what the spec asks for; axes in ``spec.free_dims`` may have any extent."""
+    want = tuple(spec.shape)
+    return len(found) == len(want) and all(f == w or i in spec.free_dims for i, (f, w) in enumerate(zip(found, want)))
+
+
 def check_names_and_shapes(source, expected: dict):
     """Raise one WeightError listing every mismatch between ``source`` and ``expected``
     (name -> WeightSpec)."""
@@ -24,7 +30,7 @@ def check_names_and_shapes(source, expected: dict):
     unexpected = sorted(have - set(expected))
     wrong = []
     for n, s in expected.items():
-        if n in have and tuple(source.shape(n)) != tuple(s.shape):
+        if n in have and not same_shape(tuple(source.shape(n)), s):
             wrong.append(f"{n}: expected {tuple(s.shape)}, found {tuple(source.shape(n))}")
         elif n in have:
             dt = source.dtype(n)

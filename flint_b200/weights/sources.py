@@ -27,12 +27,15 @@ class WeightSpec:
     ``"vector"`` (norm scales and biases: widened to float32, which is exact), or
     ``"table"`` (integer table, kept as int32).
     init: how the random source fills it: ``"normal"`` N(0, std), ``"gamma"`` 1+N(0, 0.1).
+    free_dims: axes whose extent the checkpoint decides (a low rank, say); ``shape`` holds the extent the random
+    source uses there, and the part checks what it finds when it receives the tensor.
     """
     shape: tuple
     role: str = "matrix"
     init: str = "normal"
     std: float = 0.02
     optional: bool = False
+    free_dims: tuple = ()
 
 
 class SafetensorsSource:

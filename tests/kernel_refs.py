@@ -21,6 +21,8 @@ def _act(g, name):
         return 0.5 * g * (1.0 + torch.erf(g / math.sqrt(2.0)))
     if name == "none":
         return g
+    if name == "relu2":
+        return torch.clamp(g, min=0) ** 2
     return 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
 
 
@@ -247,13 +249,15 @@ class RefOps:
         cache.v[pages, :, p % P, :] = v.to(cache.v.dtype)
 
     def sink_attention(self, q, cache, step, out, nq, nkv, hd, vd, window, keep_first, sinks, scale, splits=None,
-                       tiling=None, rows=None):
+                       tiling=None, rows=None, chunk=0):
         T, P, G = q.shape[0], cache.page_size, nq // nkv
         qq = q.to(self.cd).view(T, nq, hd)
         res = torch.zeros(T, nq, vd, dtype=self.cd)
         for t in range(T):
             p = int(step.pos[t])
             lo = max(0, p + 1 - window) if window else 0
+            if chunk:
+                lo = (p // chunk) * chunk
             js = torch.cat([torch.arange(0, min(keep_first, lo)), torch.arange(lo, p + 1)])
             pages = cache.block_table[int(step.slot[t]), js // P].long()
             assert (pages >= 0).all(), f"row {t}: key without a page"
@@ -309,6 +313,181 @@ class RefOps:
         x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
         y = x.reshape(T, H * V) * norm_w.to(self.cd) * torch.sigmoid(gate.to(self.cd))
         out.copy_(y.to(out.dtype))
+
+    # ------------------------------------------------------------------ state carried from token to token
+    @staticmethod
+    def _runs(pos, slot):
+        """[(first row, one past the last row)] of every request's rows in the batch."""
+        T, runs, a = pos.numel(), [], 0
+        for t in range(1, T + 1):
+            if t == T or int(slot[t]) != int(slot[t - 1]) or int(pos[t]) != int(pos[t - 1]) + 1:
+                runs.append((a, t))
+                a = t
+        return runs
+
+    def short_conv(self, u, col0, w, bias, act, pos, slot, state, y):
+        C, taps = w.shape
+        x = u[:, col0:col0 + C].to(self.cd)
+        ww = w.to(self.cd)
+        res = torch.zeros(x.shape, dtype=self.cd)
+        for a, b in self._runs(pos, slot):
+            sl, p0 = int(slot[a]), int(pos[a])
+            past = torch.zeros(taps - 1, C, dtype=self.cd)       # inputs of positions p0 - taps + 1 .. p0 - 1
+            for d in range(1, taps):
+                if p0 - d >= 0:
+                    r = (p0 - d) % (taps - 1)
+                    past[taps - 1 - d] = state[sl, r * C:(r + 1) * C].to(self.cd)
+            seq = torch.cat([past, x[a:b]], 0)
+            for j in range(taps):
+                res[a:b] += ww[:, j] * seq[j:j + b - a]
+            for t in range(max(a, b - (taps - 1)), b):
+                r = int(pos[t]) % (taps - 1)
+                state[sl, r * C:(r + 1) * C] = x[t].to(state.dtype)
+        if bias is not None:
+            res = res + bias.to(self.cd)
+        y.copy_(_act(res, act).to(y.dtype))
+
+    def delta_prepare(self, y, b, a, dt_bias, a_log, qk, decay, beta, H, G, D, unit_eps):
+        T = y.shape[0]
+        x = y[:, :2 * G * D].to(self.cd).view(T, 2 * G, D)
+        x = x / torch.sqrt((x * x).sum(-1, keepdim=True) + unit_eps)
+        x[:, :G] = x[:, :G] * D ** -0.5
+        qk.copy_(x.reshape(T, 2 * G * D).to(qk.dtype))
+        beta.copy_(torch.sigmoid(b.to(self.cd)).to(beta.dtype))
+        sp = torch.nn.functional.softplus(a.to(self.cd) + dt_bias.to(self.cd), threshold=30.0).view(T, H, D)
+        decay.copy_(torch.exp(-torch.exp(a_log.to(self.cd)).view(1, H, 1) * sp).reshape(T, H * D).to(decay.dtype))
+
+    def ssd_prepare(self, raw, dt_bias, a_log, dt, decay):
+        d = torch.nn.functional.softplus(raw.to(self.cd) + dt_bias.to(self.cd), threshold=30.0)
+        dt.copy_(d.to(dt.dtype))
+        decay.copy_(torch.exp(-torch.exp(a_log.to(self.cd)) * d).to(decay.dtype))
+
+    def recurrence_scan(self, q, k, v, decay, delta, beta, dt, skip, slot, seq_start, n_seq, state, out, H, G, D, V):
+        T = q.shape[0]
+        qq, kk, vv = q.to(self.cd).view(T, G, D), k.to(self.cd).view(T, G, D), v.to(self.cd).view(T, H, V)
+        dec = decay.to(self.cd).view(T, H, D) if delta else decay.to(self.cd)
+        starts = list(range(n_seq + 1)) if seq_start is None else seq_start.tolist()
+        res = torch.zeros(T, H, V, dtype=self.cd)
+        for e in range(n_seq):
+            if starts[e + 1] <= starts[e]:
+                continue
+            sl = int(slot[starts[e]])
+            S = state[sl, :H * D * V].to(self.cd).view(H, D, V).clone()
+            for t in range(starts[e], starts[e + 1]):
+                for h in range(H):
+                    g = h // (H // G)
+                    if delta:
+                        S[h] = dec[t, h][:, None] * S[h]
+                        u = beta[t, h].to(self.cd) * (vv[t, h] - S[h].T @ kk[t, g])
+                    else:
+                        S[h] = dec[t, h] * S[h]
+                        u = dt[t, h].to(self.cd) * vv[t, h]
+                    S[h] = S[h] + torch.outer(kk[t, g], u)
+                    res[t, h] = S[h].T @ qq[t, g]
+                    if skip is not None:
+                        res[t, h] = res[t, h] + skip[h].to(self.cd) * vv[t, h]
+            state[sl, :H * D * V] = S.reshape(-1).to(state.dtype)
+        out.copy_(res.reshape(T, H * V).to(out.dtype))
+
+    def gated_norm(self, o, gate, gate_act, gate_first, w, eps, groups, out):
+        T, N = o.shape
+        x = o.to(self.cd)
+        g = gate.to(self.cd)
+        g = g / (1.0 + torch.exp(-g)) if gate_act == "silu" else torch.sigmoid(g)
+        if gate_first:
+            x = x * g
+        x = x.view(T, groups, N // groups)
+        x = (x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)).reshape(T, N)
+        x = x * w.to(self.cd).repeat(N // w.numel())
+        if not gate_first:
+            x = x * g
+        out.copy_(x.to(out.dtype))
+
+    def branch_mean(self, branches, weights, eps, out):
+        acc = torch.zeros(out.shape, dtype=self.cd)
+        for (part, bias), w in zip(branches, weights):
+            y = part.to(self.cd).sum(0)
+            if bias is not None:
+                y = y + bias.to(self.cd)
+            acc += y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps) * w.to(self.cd)
+        out.copy_((acc / len(branches)).to(out.dtype))
+
+    def post_norm(self, x, partials, bias, scale, residual_scale, gamma, beta, eps, mode, out_copy=None):
+        y = partials.to(self.cd).sum(0)
+        if bias is not None:
+            y = y + bias.to(self.cd)
+        if scale is not None:
+            y = y * scale.to(self.cd)
+        v = residual_scale * x.to(self.cd) + y
+        if mode == "layer":
+            v = v - v.mean(-1, keepdim=True)
+        v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * gamma.to(self.cd)
+        if beta is not None:
+            v = v + beta.to(self.cd)
+        x.copy_(v.to(x.dtype))
+        if out_copy is not None:
+            out_copy.copy_(v.to(torch.float32).to(out_copy.dtype))
+
+    def depth_mix(self, history, n, w, h, out_copy=None):
+        history[n - 1].copy_(h)
+        acc = (history[:n].to(self.cd) * w[:n].to(self.cd).view(n, 1, 1)).sum(0)
+        h.copy_(acc.to(h.dtype))
+        if out_copy is not None:
+            out_copy.copy_(acc.to(torch.float32).to(out_copy.dtype))
+
+    def softcap(self, x, cap):
+        x.copy_((cap * torch.tanh(x.to(self.cd) / cap)).to(x.dtype))
+
+    def cast_rows(self, x, out):
+        out.copy_(x.to(out.dtype))
+
+    @staticmethod
+    def _turn(h, cos, sin, style, sign=1.0):
+        """h [T, heads, n] with the leading 2 * cos.shape[-1] dims rotated by the angles of cos, sin [T, n / 2]."""
+        rot = 2 * cos.shape[-1]
+        if rot == 0:
+            return h
+        c, s_ = cos[:, None, :], sign * sin[:, None, :]
+        if style == "interleaved":
+            a, b = h[..., 0:rot:2], h[..., 1:rot:2]
+            both = torch.stack([a * c - b * s_, b * c + a * s_], -1).reshape(*h.shape[:-1], rot)
+        else:
+            a, b = h[..., :rot // 2], h[..., rot // 2:rot]
+            both = torch.cat([a * c - b * s_, b * c + a * s_], -1)
+        return torch.cat([both, h[..., rot:]], -1)
+
+    def qk_norm_write(self, y, q_norm, k_norm, eps, pos, slot, cos, sin, rot, style, v_cos, v_sin, v_style, q_out, cache,
+                      nq, nkv, hd, vd, status):
+        T = y.shape[0]
+        x = y.to(self.cd)
+        p = pos.long()
+        q = x[:, :nq * hd].view(T, nq, hd)
+        k = x[:, nq * hd:(nq + nkv) * hd].view(T, nkv, hd)
+        v = x[:, (nq + nkv) * hd:(nq + nkv) * hd + nkv * vd].view(T, nkv, vd)
+        if q_norm is not None:
+            q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps) * q_norm.to(self.cd)
+            k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps) * k_norm.to(self.cd)
+        if rot:
+            q = self._turn(q, cos[p].to(self.cd), sin[p].to(self.cd), style)
+            k = self._turn(k, cos[p].to(self.cd), sin[p].to(self.cd), style)
+        if v_cos is not None:
+            v = self._turn(v, v_cos[p].to(self.cd), v_sin[p].to(self.cd), v_style)
+        q_out.copy_(q.reshape(T, nq * hd).to(q_out.dtype))
+        P = cache.page_size
+        pages = cache.block_table[slot.long(), p // P].long()
+        assert (pages >= 0).all(), "write to a position without a page"
+        cache.k[pages, :, p % P, :] = k.to(cache.k.dtype)
+        cache.v[pages, :, p % P, :] = v.to(cache.v.dtype)
+
+    def head_finish(self, attn, pos, v_cos, v_sin, v_style, gate, out, nq, vd):
+        T = attn.shape[0]
+        x = attn.to(self.cd).view(T, nq, vd)
+        if v_cos is not None:
+            p = pos.long()
+            x = self._turn(x, v_cos[p].to(self.cd), v_sin[p].to(self.cd), v_style, sign=-1.0)
+        if gate is not None:
+            x = x * torch.sigmoid(gate.to(self.cd))[:, :, None]
+        out.copy_(x.reshape(T, nq * vd).to(out.dtype))
 
     # ------------------------------------------------------------------ sigmoid router, plain experts
     def router_sigmoid(self, x, wr, E, top, expert_ids, scores, weights, logits_out=None):
