@@ -344,6 +344,8 @@ class Model:
                     carry = None
                 # history[i + 1] <- h, then h <- sum_j w[j] history[j] over the i + 2 sets of rows so far
                 ops.depth_mix(history, i + 2, self.depth_weights[i], h, out_copy=copy)
+                if step.record is not None:
+                    step.record.setdefault("handed_on", []).append(h.clone())
                 if copy is not None:
                     step.shared["rows"] = (h, {copy.dtype: copy})
         R = step.n_want
