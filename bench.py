@@ -480,6 +480,128 @@ GEPADRA_SIZES = {
 }
 
 
+def tefovik_config(width, heads, kv_heads, dim, vdim, chunk, rot, d_heads, d_kv_heads, d_dim, d_vdim, s_heads, s_vdim, s_state,
+                   s_groups, ff, layers, vocab, taps=4):
+    """A Tefovik configuration of ``layers`` layers: the even ones an attention branch (runs of ``chunk`` positions) beside
+    a gated delta rule, the odd ones a state-space mixer; every layer with the ungated feed-forward."""
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            kind = "parallel"
+            m = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "conv": taps,
+                          "mask": {"size": chunk}, "rot": {"dims": rot, "base": 5e5}},
+                 "right": {"heads": d_heads, "kv_heads": d_kv_heads, "dim": d_dim, "vdim": d_vdim, "conv": taps}}
+        else:
+            kind = "mamba2"
+            m = {"heads": s_heads, "vdim": s_vdim, "state": s_state, "groups": s_groups, "norm_groups": s_groups, "conv": taps}
+        out.append({"type": kind, "mixer": m, "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Tefovik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "postln_alpha": 2.0,
+            "logit_softcap": 30.0, "layers": out}
+
+
+# layer sizes that resemble real models of this kind, beside a Gepadra of equal width whose attention layers have the
+# same heads and whose window is as long as the run, whose mLSTM heads hold a state of the delta rule's shape, and
+# whose experts (two routed and the shared one) have the feed-forward's parameters
+TEFOVIK_SIZES = {
+    "2048x16": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, chunk=1024, rot=64, d_heads=16, d_kv_heads=8, d_dim=128,
+                    d_vdim=128, s_heads=64, s_vdim=64, s_state=128, s_groups=8, ff=8192,
+                    gepadra=dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep=8, rot=64, m_heads=16,
+                                 m_dim=128, m_vdim=128, ff=2720, experts=8, top=2, shared=2720, dense_ff=5440, every=2)),
+    "4096x32": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, chunk=1024, rot=64, d_heads=32, d_kv_heads=16, d_dim=128,
+                    d_vdim=128, s_heads=128, s_vdim=64, s_state=128, s_groups=8, ff=16384,
+                    gepadra=dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, keep=8, rot=64, m_heads=32,
+                                 m_dim=128, m_vdim=128, ff=5472, experts=8, top=2, shared=5472, dense_ff=10944, every=2)),
+}
+
+FP32_FMA_LANES = 148 * 128      # float32 lanes of the chip; times 2 flops, times the clock: the rate the scans are put against
+
+
+def run_tefovik_pair(args, pk, rng):
+    """Prefill and decode of Tefovik at layer sizes that resemble real models, beside Gepadra at equal width, heads and
+    state shape: tokens/s, and for the attention and recurrence kernels of both the time a layer and the distance from
+    the roofline (decode: cache or state bytes over the measured copy bandwidth; prefill attention: flops over the
+    sustained library product rate; prefill recurrences, which walk tokens in float32 on the plain pipes: flops over
+    the chip's float32 multiply-add rate at its highest clock)."""
+    import torch
+    layers = args.layers or 8
+    vocab = args.vocab or 32064
+    batch, ctx = args.batch, args.prompt_tokens
+    fp32_rate = FP32_FMA_LANES * 2 * 1.965e9
+    out = {"design": "Tefovik", "beside": "Gepadra", "layers": layers, "batch": batch, "prompt_tokens": ctx, "dtype": "bf16",
+           "data": "synthetic: seeded random weights, uniform-random token ids",
+           "peaks": {**{k: pk[k] for k in ("hbm_gbs", "bf16_tflops_sustained", "source")},
+                     "fp32_tflops_nominal": round(fp32_rate / 1e12, 1)}, "sizes": {}}
+    for name, sz in TEFOVIK_SIZES.items():
+        if args.design_sizes and name not in args.design_sizes:
+            continue
+        cfgs = {"tefovik": tefovik_config(**{k: v for k, v in sz.items() if k != "gepadra"}, layers=layers, vocab=vocab),
+                "gepadra": gepadra_config(**sz["gepadra"], layers=layers, vocab=vocab)}
+        row = {}
+        for which, cfg in cfgs.items():
+            cfg.setdefault("vocab_size", cfg.get("vocab"))
+            model = build_model(cfg, max(batch, 1), ctx + 256)
+            pre_ms = run_prefill(model, cfg, ctx, reps=3, warmup=3, rng=rng)
+            dec = run_decode(model, cfg, batch, ctx, args.steps, max(args.warmup, 3), rng, count_experts=False)
+            pre_t, dec_t, _ = profile_tables(model, cfg, batch, ctx, rng)
+            kv = ctx + 2
+            mixers = [l.parts["mixer"] for l in model.layers]
+            if which == "tefovik":
+                pairs = [m for m in mixers if hasattr(m, "branches")]
+                att, rec = (dict(pairs[0].branches)[n] for n in ("left", "right"))
+                ssd = next(m for m in mixers if not hasattr(m, "branches"))
+                seen = lambda k: (k - 1) % att.chunk + 1 if att.chunk else k
+                n_att = len(pairs)
+                # state elements of a layer's recurrence, and the multiply-adds (x2 flops) plus multiplies an element costs a token
+                scans = {"delta": (rec.H * rec.D * rec.V, 9, n_att), "ssd": (ssd.H * ssd.N * ssd.V, 5, layers - n_att)}
+                names = ("flint_sink_attention", "flint_qk_norm_write", "flint_head_finish", "flint_short_conv", "flint_recurrence_scan",
+                         "flint_delta_prepare", "flint_ssd_prepare", "flint_gated_norm", "flint_branch_mean", "flint_post_norm",
+                         "flint_depth_mix", "flint_row_act")
+            else:
+                att = next(m for m in mixers if hasattr(m, "keep_first"))
+                rec = next(m for m in mixers if hasattr(m, "cap"))
+                n_att = sum(1 for m in mixers if hasattr(m, "keep_first"))
+                seen = lambda k: min(k, att.window + att.keep_first) if att.window else k
+                scans = {"mlstm": (rec.H * (rec.D * rec.V + rec.D + 1), 5, layers - n_att)}
+                names = ("flint_sink_attention", "flint_qkv_write", "flint_mlstm", "flint_row_norm", "flint_row_act")
+            att_bytes = batch * seen(kv) * att.nkv * (att.hd + att.vd) * 2
+            att_flops = sum(2 * att.nq * (att.hd + att.vd) * seen(k) for k in range(1, ctx + 1))
+            kern = {}
+            for kind, table in (("prefill", pre_t), ("decode", dec_t)):
+                for kname, (n, ms) in sorted(table.items()):
+                    if not kname.startswith(names):
+                        continue
+                    scan = next((s for s in scans if kname.startswith(("flint_recurrence_scan " + s, "flint_mlstm_scan"))), None)
+                    per = layers
+                    if scan is not None:
+                        per = scans[scan][2]
+                    elif any(t in kname for t in ("attention", "qkv_write", "qk_norm_write", "head_finish", "delta_prepare", "branch_mean")):
+                        per = n_att
+                    elif "mlstm" in kname or "ssd_prepare" in kname:
+                        per = layers - n_att
+                    secs = ms / per * 1e-3
+                    e = {"launches": n, "us_per_layer": round(ms * 1000.0 / per, 2)}
+                    if scan is not None:
+                        elems, flops, _ = scans[scan]
+                        if kind == "decode":        # the state is read and written once a token
+                            e["frac_of_copy_bandwidth"] = round(batch * elems * 4 * 2 / secs / 1e9 / pk["hbm_gbs"], 4)
+                        else:
+                            e["frac_of_fp32_rate"] = round(ctx * elems * flops / secs / fp32_rate, 4)
+                            e["ns_per_token"] = round(secs * 1e9 / ctx, 1)
+                    elif kname.startswith("flint_sink_attention"):
+                        if kind == "decode":
+                            e["frac_of_copy_bandwidth"] = round(att_bytes / secs / 1e9 / pk["hbm_gbs"], 4)
+                        else:
+                            e["frac_of_sustained_product_rate"] = round(att_flops / secs / (pk["bf16_tflops_sustained"] * 1e12), 4)
+                    kern[f"{kind}: {kname}"] = e
+            row[which] = {"prefill_tok_s": round(ctx * 1000.0 / pre_ms, 1), "prefill_ms": round(pre_ms, 3),
+                          "decode_tok_s": round(dec["tok_s"], 1), "decode_ms_per_step": round(dec["ms"], 4),
+                          "decode_launches": dec["launches"], "weight_gb": round(model.weight_bytes() / 1e9, 2), "kernels": kern}
+            del model
+            torch.cuda.empty_cache()
+        out["sizes"][name] = row
+    return out
+
+
 def run_design_pair(args, pk, rng):
     """Prefill and decode of Puledra or Gepadra at layer sizes that resemble real models, beside Phi-MoE at equal width, heads
     and active expert parameters: tokens/s, and for the attention kernels of both the time a layer and the
@@ -800,9 +922,9 @@ def main():
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the default run: decode at batch 1 and 8 with contexts of 16,384 and 65,536 tokens, "
                          "batch 1 with 131,008, and batch 128 and 256 with 2,048, each with its roofline fraction")
-    ap.add_argument("--design", choices=["puledra", "gepadra"], default=None,
-                    help="prefill and decode of this design at layer sizes that resemble real models, beside Phi-MoE at "
-                         "equal width, heads and active expert parameters, with the attention kernels' shares of the peaks")
+    ap.add_argument("--design", choices=["puledra", "gepadra", "tefovik"], default=None,
+                    help="prefill and decode of this design at layer sizes that resemble real models, beside the closest "
+                         "earlier model at equal sizes (Phi-MoE; for tefovik Gepadra), with its kernels' shares of the peaks")
     ap.add_argument("--design-sizes", nargs="+", default=None, help="which of the design's size points to run")
     ap.add_argument("--profile", action="store_true",
                     help="print per-kernel device times of one prefill and one decode step to stderr and exit")
@@ -834,7 +956,7 @@ def main():
         print(json.dumps(run_tiny(args.tiny)))
         return 0
     if args.design:
-        print(json.dumps(run_design_pair(args, pk, rng)))
+        print(json.dumps(run_tefovik_pair(args, pk, rng) if args.design == "tefovik" else run_design_pair(args, pk, rng)))
         return 0
     if args.sweep:
         print(json.dumps(run_sweep(cfg, pk, rng, max(8, args.steps // 4), warmup)))

@@ -980,6 +980,7 @@ class CudaOps:
                 raise KernelError("recurrence_scan: seq_start must have one entry more than there are requests")
         elif n_seq != T:
             raise KernelError("recurrence_scan: without seq_start every request brings one row")
+        self._label = f"{'delta' if delta else 'ssd'} H{H} D{D} V{V}"
         self._run("recurrent", "flint_recurrence_scan", _ptr(q), c_longlong(q.stride(0)), _ptr(k), c_longlong(k.stride(0)),
                   _ptr(v), c_longlong(v.stride(0)), _ptr(decay), c_int(1 if delta else 0), _ptr(w1), _ptr(skip), _ptr(slot),
                   _ptr(seq_start), c_int(n_seq), _ptr(state), c_longlong(state.stride(0)), _ptr(out), c_int(H), c_int(G),
