@@ -126,11 +126,19 @@ __device__ __forceinline__ void copy4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
+__device__ __forceinline__ void copy16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+constexpr int SEG = RPT + 4;     // floats between the rows of neighbouring lanes of a column: their 16-byte reads miss each other's banks
+
 // TPC: threads per column (D <= 32 TPC).  DELTA: the gated delta rule (a decay per key channel, the write corrected
 // by what the state already returns for the key), else the state-space form (one decay per head, plain write).
 // q, k [T, G D] and v [T, H V] are float32 views with row strides; decay [T, H D] (DELTA) or [T, H]; w1 [T, H]: beta
 // (DELTA) or dt; skip [H] or null.  seq_start [n_seq + 1] or null (row e is request e).  Grid: (column blocks, H, n_seq).
-template <int TPC, bool DELTA>
+// VEC: every row of q, k, v and decay starts on a 16-byte boundary and D and V are multiples of 4, so the operands are
+// staged 16 bytes a copy; else 4 bytes a copy.  Both leave the same numbers in the same places.
+template <int TPC, bool DELTA, bool VEC>
 __global__ void __launch_bounds__(SCAN_THREADS)
 recurrence_scan_kernel(const float* __restrict__ q, long long q_stride, const float* __restrict__ k, long long k_stride,
                        const float* __restrict__ v, long long v_stride, const float* __restrict__ decay,
@@ -138,17 +146,17 @@ recurrence_scan_kernel(const float* __restrict__ q, long long q_stride, const fl
                        const int* __restrict__ seq_start, float* __restrict__ state, long long state_stride,
                        float* __restrict__ o, int H, int G, int D, int V, int TB) {
   extern __shared__ __align__(16) float sm[];
-  pdl_launch();
-  constexpr int DP = TPC * RPT;                  // key dims, padded
+  constexpr int DP = TPC * SEG;                  // floats of a staged vector of key dims: lane s of a column reads from s SEG
+  constexpr int NV = DELTA ? 3 : 2;              // staged vectors a token: q, k (and the decay per channel)
   constexpr int COLS = SCAN_THREADS / TPC;       // columns a block takes
   const int tid = threadIdx.x, sub = tid % TPC, col = blockIdx.x * COLS + tid / TPC;
   const int h = blockIdx.y, e = blockIdx.z, kh = h / (H / G);
   const int r0 = seq_start ? seq_start[e] : e, r1 = seq_start ? seq_start[e + 1] : e + 1;
   if (r1 <= r0) return;
-  // a stage: TB tokens of q, k (and decay per channel) padded to DP, the columns' values, and two numbers a token
-  const int per_tok = (DELTA ? 3 : 2) * DP + COLS + 4;     // a multiple of 4: the operands are read as float4
+  // a stage: TB tokens of q, k (and decay per channel), the columns' values, and two numbers a token
+  const int per_tok = NV * DP + COLS + 4;        // a multiple of 4: the operands are read as float4
   float* stage[2] = {sm, sm + (size_t)TB * per_tok};
-  for (int i = tid; i < 2 * TB * per_tok; i += SCAN_THREADS) {      // padding: q = k = 0, decay = 1
+  for (int i = tid; i < 2 * TB * per_tok; i += SCAN_THREADS) {      // dims beyond D: q = k = 0, decay = 1
     const int w = i % per_tok;
     sm[i] = (DELTA && w >= 2 * DP && w < 3 * DP) ? 1.f : 0.f;
   }
@@ -162,23 +170,44 @@ recurrence_scan_kernel(const float* __restrict__ q, long long q_stride, const fl
     const int d = sub * RPT + i;
     S[i] = (live && d < D) ? S_g[(size_t)d * V + col] : 0.f;
   }
+  const int c0 = blockIdx.x * COLS, nc = min(COLS, V - c0);
+  const float* q_h = q + (size_t)kh * D;
+  const float* k_h = k + (size_t)kh * D;
+  const float* g_h = DELTA ? decay + (size_t)h * D : nullptr;
+  const float* v_h = v + (size_t)h * V + c0;
   auto fetch = [&](int t0, int st) {
     const int n = min(TB, r1 - t0);
     float* base = stage[st];
-    for (int i = tid; i < n * D; i += SCAN_THREADS) {
-      const int tt = i / D, d = i % D, t = t0 + tt;
-      float* dst = base + (size_t)tt * per_tok;
-      copy4(dst + d, q + (size_t)t * q_stride + (size_t)kh * D + d);
-      copy4(dst + DP + d, k + (size_t)t * k_stride + (size_t)kh * D + d);
-      if (DELTA) copy4(dst + 2 * DP + d, decay + ((size_t)t * H + h) * D + d);
-    }
-    const int c0 = blockIdx.x * COLS, nc = min(COLS, V - c0);
-    for (int i = tid; i < n * nc; i += SCAN_THREADS) {
-      const int tt = i / nc, c = i % nc;
-      copy4(base + (size_t)tt * per_tok + (DELTA ? 3 : 2) * DP + c, v + (size_t)(t0 + tt) * v_stride + (size_t)h * V + c0 + c);
+    if (VEC) {
+      // piece j of a token: 16 bytes of q, then of k, then of the decay, then of the values
+      const int d4 = D >> 2, pieces = NV * d4 + (nc >> 2);
+      for (int j = tid; j < pieces; j += SCAN_THREADS) {
+        int a = 0, x = j;                        // which vector, which piece of it
+        if (x >= d4) { x -= d4; a = 1; }
+        if (a == 1 && x >= d4) { x -= d4; a = 2; }
+        if (DELTA && a == 2 && x >= d4) { x -= d4; a = 3; }
+        const bool val = a == NV;
+        const int d = 4 * x;
+        const int off = val ? NV * DP + d : a * DP + (d / RPT) * SEG + d % RPT;
+        const float* src = val ? v_h + d : (a == 0 ? q_h : a == 1 ? k_h : g_h) + d;
+        const long long stride = val ? v_stride : a == 0 ? q_stride : a == 1 ? k_stride : (long long)H * D;
+        for (int tt = 0; tt < n; ++tt) copy16(base + (size_t)tt * per_tok + off, src + (size_t)(t0 + tt) * stride);
+      }
+    } else {
+      for (int i = tid; i < n * D; i += SCAN_THREADS) {
+        const int tt = i / D, d = i % D, t = t0 + tt;
+        float* dst = base + (size_t)tt * per_tok + (d / RPT) * SEG + d % RPT;
+        copy4(dst, q_h + (size_t)t * q_stride + d);
+        copy4(dst + DP, k_h + (size_t)t * k_stride + d);
+        if (DELTA) copy4(dst + 2 * DP, g_h + (size_t)t * H * D + d);
+      }
+      for (int i = tid; i < n * nc; i += SCAN_THREADS) {
+        const int tt = i / nc, c = i % nc;
+        copy4(base + (size_t)tt * per_tok + NV * DP + c, v_h + (size_t)(t0 + tt) * v_stride + c);
+      }
     }
     for (int tt = tid; tt < n; tt += SCAN_THREADS) {
-      float* dst = base + (size_t)tt * per_tok + (DELTA ? 3 : 2) * DP + COLS;
+      float* dst = base + (size_t)tt * per_tok + NV * DP + COLS;
       copy4(dst, w1 + (size_t)(t0 + tt) * H + h);
       if (!DELTA) copy4(dst + 1, decay + (size_t)(t0 + tt) * H + h);
     }
@@ -198,23 +227,25 @@ recurrence_scan_kernel(const float* __restrict__ q, long long q_stride, const fl
     const int n = min(TB, r1 - t0);
     for (int tt = 0; tt < n; ++tt) {
       const float* tok = stage[st] + (size_t)tt * per_tok;
-      const float* qs = tok + sub * RPT;
-      const float* ks = tok + DP + sub * RPT;
-      const float* rest = tok + (DELTA ? 3 : 2) * DP;
+      const float4* q4 = reinterpret_cast<const float4*>(tok + sub * SEG);
+      const float4* k4 = reinterpret_cast<const float4*>(tok + DP + sub * SEG);
+      const float* rest = tok + NV * DP;
       const float vj = rest[tid / TPC], w = rest[COLS];
+      float4 kr[RPT / 4];                        // the key's dims of this lane, read once for both passes
+#pragma unroll
+      for (int i = 0; i < RPT / 4; ++i) kr[i] = k4[i];
       float u;
       if (DELTA) {
-        const float4* g4 = reinterpret_cast<const float4*>(tok + 2 * DP + sub * RPT);
-        const float4* k4 = reinterpret_cast<const float4*>(ks);
-        float dot0 = 0.f, dot1 = 0.f;
+        const float4* g4 = reinterpret_cast<const float4*>(tok + 2 * DP + sub * SEG);
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
         for (int i = 0; i < RPT / 4; ++i) {
-          const float4 gg = g4[i], kk = k4[i];
+          const float4 gg = g4[i];
           S[4 * i] *= gg.x; S[4 * i + 1] *= gg.y; S[4 * i + 2] *= gg.z; S[4 * i + 3] *= gg.w;
-          dot0 = fmaf(S[4 * i], kk.x, dot0); dot1 = fmaf(S[4 * i + 1], kk.y, dot1);
-          dot0 = fmaf(S[4 * i + 2], kk.z, dot0); dot1 = fmaf(S[4 * i + 3], kk.w, dot1);
+          d0 = fmaf(S[4 * i], kr[i].x, d0); d1 = fmaf(S[4 * i + 1], kr[i].y, d1);
+          d2 = fmaf(S[4 * i + 2], kr[i].z, d2); d3 = fmaf(S[4 * i + 3], kr[i].w, d3);
         }
-        float dot = dot0 + dot1;
+        float dot = (d0 + d1) + (d2 + d3);
 #pragma unroll
         for (int m = 1; m < TPC; m <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
         u = w * (vj - dot);
@@ -224,26 +255,25 @@ recurrence_scan_kernel(const float* __restrict__ q, long long q_stride, const fl
         for (int i = 0; i < RPT; ++i) S[i] *= a;
         u = w * vj;
       }
-      float out0 = 0.f, out1 = 0.f;
-      {
-        const float4* k4 = reinterpret_cast<const float4*>(ks);
-        const float4* q4 = reinterpret_cast<const float4*>(qs);
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < RPT / 4; ++i) {
-          const float4 kk = k4[i], qq = q4[i];
-          S[4 * i] = fmaf(kk.x, u, S[4 * i]); S[4 * i + 1] = fmaf(kk.y, u, S[4 * i + 1]);
-          S[4 * i + 2] = fmaf(kk.z, u, S[4 * i + 2]); S[4 * i + 3] = fmaf(kk.w, u, S[4 * i + 3]);
-          out0 = fmaf(S[4 * i], qq.x, out0); out1 = fmaf(S[4 * i + 1], qq.y, out1);
-          out0 = fmaf(S[4 * i + 2], qq.z, out0); out1 = fmaf(S[4 * i + 3], qq.w, out1);
-        }
+      for (int i = 0; i < RPT / 4; ++i) {
+        const float4 qq = q4[i];
+        S[4 * i] = fmaf(kr[i].x, u, S[4 * i]); S[4 * i + 1] = fmaf(kr[i].y, u, S[4 * i + 1]);
+        S[4 * i + 2] = fmaf(kr[i].z, u, S[4 * i + 2]); S[4 * i + 3] = fmaf(kr[i].w, u, S[4 * i + 3]);
+        o0 = fmaf(S[4 * i], qq.x, o0); o1 = fmaf(S[4 * i + 1], qq.y, o1);
+        o2 = fmaf(S[4 * i + 2], qq.z, o2); o3 = fmaf(S[4 * i + 3], qq.w, o3);
       }
-      float out = out0 + out1;
+      float out = (o0 + o1) + (o2 + o3);
 #pragma unroll
       for (int m = 1; m < TPC; m <<= 1) out += __shfl_xor_sync(0xffffffffu, out, m);
       if (live && sub == 0) o[(size_t)(t0 + tt) * H * V + (size_t)h * V + col] = fmaf(skip_h, vj, out);
     }
     __syncthreads();          // the stage is refilled in the next round
   }
+  // Only now may the kernel behind this one start: its blocks would wait on the SMs beside the walk's few warps for
+  // as long as the walk takes (a prompt of 2,048 tokens ran twice as long with the release at the top).
+  pdl_launch();
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
     const int d = sub * RPT + i;
@@ -522,14 +552,22 @@ extern "C" int flint_recurrence_scan(const float* q, long long q_stride, const f
   if (G <= 0 || H % G) return fail("recurrence_scan: %d heads do not divide into %d key heads", H, G);
   if (n_seq > 65535 || H > 65535) return fail("recurrence_scan: too many requests or heads");
   const int tpc = D <= 32 ? 1 : D <= 64 ? 2 : D <= 128 ? 4 : 8;
-  const int dp = tpc * RPT, cols = SCAN_THREADS / tpc;
-  const int tb = dp <= 64 ? 16 : dp <= 128 ? 8 : 4;
+  const int dp = tpc * SEG, cols = SCAN_THREADS / tpc;
+  const int tb = tpc <= 2 ? 16 : tpc <= 4 ? 8 : 4;
   const size_t smem = (size_t)2 * tb * ((delta ? 3 : 2) * dp + cols + 4) * sizeof(float);
   const dim3 grid((unsigned)((V + cols - 1) / cols), (unsigned)H, (unsigned)n_seq), block(SCAN_THREADS);
-#define SCAN(TPC, DELTA)                                                                                              \
-  launch_pdl(recurrence_scan_kernel<TPC, DELTA>, grid, block, smem, stream, q, q_stride, k, k_stride, v, v_stride, decay, \
-             w1, skip, slot, seq_start, state, state_stride, o, H, G, D, V, tb)
-#define SCAN_T(TPC) do { if (delta) SCAN(TPC, true); else SCAN(TPC, false); } while (0)
+  // 16-byte copies need every staged row to start on such a boundary
+  auto lined = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  const bool vec = D % 4 == 0 && V % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && v_stride % 4 == 0 && lined(q) &&
+                   lined(k) && lined(v) && (!delta || lined(decay));
+#define SCAN(TPC, DELTA, VEC)                                                                                          \
+  launch_pdl(recurrence_scan_kernel<TPC, DELTA, VEC>, grid, block, smem, stream, q, q_stride, k, k_stride, v, v_stride, \
+             decay, w1, skip, slot, seq_start, state, state_stride, o, H, G, D, V, tb)
+#define SCAN_T(TPC)                                                                                       \
+  do {                                                                                                    \
+    if (delta) { if (vec) SCAN(TPC, true, true); else SCAN(TPC, true, false); }                           \
+    else { if (vec) SCAN(TPC, false, true); else SCAN(TPC, false, false); }                               \
+  } while (0)
   if (tpc == 1) SCAN_T(1);
   else if (tpc == 2) SCAN_T(2);
   else if (tpc == 4) SCAN_T(4);
