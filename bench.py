@@ -501,15 +501,16 @@ def tefovik_config(width, heads, kv_heads, dim, vdim, chunk, rot, d_heads, d_kv_
 
 # layer sizes that resemble real models of this kind, beside a Gepadra of equal width whose attention layers have the
 # same heads and whose window is as long as the run, whose mLSTM heads hold a state of the delta rule's shape, and
-# whose experts (two routed and the shared one) have the feed-forward's parameters
+# whose experts (two routed and the shared one) have the feed-forward's parameters.  With runs of 1,024 a decoded token
+# behind a prompt of 2,048 sees the two keys of its own run; with runs of 4,096 it sees the whole prompt.
 TEFOVIK_SIZES = {
     "2048x16": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, chunk=1024, rot=64, d_heads=16, d_kv_heads=8, d_dim=128,
                     d_vdim=128, s_heads=64, s_vdim=64, s_state=128, s_groups=8, ff=8192,
                     gepadra=dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep=8, rot=64, m_heads=16,
                                  m_dim=128, m_vdim=128, ff=2720, experts=8, top=2, shared=2720, dense_ff=5440, every=2)),
-    "4096x32": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, chunk=1024, rot=64, d_heads=32, d_kv_heads=16, d_dim=128,
+    "4096x32": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, chunk=4096, rot=64, d_heads=32, d_kv_heads=16, d_dim=128,
                     d_vdim=128, s_heads=128, s_vdim=64, s_state=128, s_groups=8, ff=16384,
-                    gepadra=dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, keep=8, rot=64, m_heads=32,
+                    gepadra=dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=4096, keep=8, rot=64, m_heads=32,
                                  m_dim=128, m_vdim=128, ff=5472, experts=8, top=2, shared=5472, dense_ff=10944, every=2)),
 }
 

@@ -37,7 +37,7 @@ __device__ __forceinline__ bool same_request(const int* pos, const int* slot, in
 }
 
 // ------------------------------------------------------------------------------------------- short convolution
-// u: float32 rows of `in_stride` floats, the convolved channels start at column col0.  One block per row.
+// u: float32 rows of `in_stride` floats, the convolved channels start at column col0.  Grid: (rows, blocks of channels).
 __global__ void short_conv_kernel(const float* __restrict__ u, long long in_stride, int col0, const float* __restrict__ w,
                                   const float* __restrict__ bias, int act, const int* __restrict__ pos,
                                   const int* __restrict__ slot, const float* __restrict__ ring, long long ring_stride,
@@ -51,7 +51,7 @@ __global__ void short_conv_kernel(const float* __restrict__ u, long long in_stri
   while (have < taps - 1 && same_request(pos, slot, t, have + 1, T)) ++have;
   const float* mine = ring + (size_t)slot[t] * ring_stride;
   const float* row = u + (size_t)t * in_stride + col0;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
     float acc = bias ? bias[c] : 0.f;
     for (int d = taps - 1; d >= 1; --d) {          // oldest first: the order of the sum does not depend on the cut
       const int q = p - d;
@@ -74,7 +74,7 @@ __global__ void short_conv_keep_kernel(const float* __restrict__ u, long long in
   if (same_request(pos, slot, t, -(taps - 1), T)) return;
   float* mine = ring + (size_t)slot[t] * ring_stride + (size_t)(pos[t] % (taps - 1)) * C;
   const float* row = u + (size_t)t * in_stride + col0;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) mine[c] = row[c];
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) mine[c] = row[c];
 }
 
 // ------------------------------------------------------------------------------------------- gated delta rule: operands
@@ -511,17 +511,24 @@ __global__ void head_finish_kernel(const TA* __restrict__ attn, const int* __res
 }  // namespace
 
 // =========================================================================================== launchers
+// Threads of a block that takes a whole row of W numbers, each summed from several partial sums: two numbers a thread,
+// so that a batch of a few rows still has many loads in flight.
+static int row_threads(int W) { return W >= 2048 ? 1024 : W >= 1024 ? 512 : W >= 512 ? 256 : 128; }
+
 extern "C" int flint_short_conv(const float* u, long long in_stride, int col0, const float* w, const float* bias, int act,
                                 const int* pos, const int* slot, float* ring, long long ring_stride, float* y, int T,
                                 int C, int taps, cudaStream_t stream) {
   if (T <= 0 || C <= 0) return 0;
   if (taps < 1 || taps > 64) return fail("short_conv: %d taps are not supported (1 to 64)", taps);
   if (taps > 1 && !ring) return fail("short_conv: a convolution over time needs the requests' state");
-  launch_pdl(short_conv_kernel, dim3((unsigned)T), dim3(C >= 1024 ? 256 : 128), 0, stream, u, in_stride, col0, w, bias, act,
-             pos, slot, (const float*)ring, ring_stride, y, T, C, taps);
+  // few rows (decoded tokens): a thread a channel, so that the rows spread over the chip; many rows: four channels a thread
+  const int threads = C >= 1024 ? 256 : 128, per = T >= 256 ? 4 : 1;
+  const dim3 grid((unsigned)T, (unsigned)min((C + threads * per - 1) / (threads * per), 65535));
+  launch_pdl(short_conv_kernel, grid, dim3(threads), 0, stream, u, in_stride, col0, w, bias, act, pos, slot,
+             (const float*)ring, ring_stride, y, T, C, taps);
   if (taps > 1)
-    launch_pdl(short_conv_keep_kernel, dim3((unsigned)T), dim3(C >= 1024 ? 256 : 128), 0, stream, u, in_stride, col0, pos,
-               slot, ring, ring_stride, T, C, taps);
+    launch_pdl(short_conv_keep_kernel, grid, dim3(threads), 0, stream, u, in_stride, col0, pos, slot, ring, ring_stride, T, C,
+               taps);
   return check_launch("short_conv");
 }
 
@@ -543,6 +550,18 @@ extern "C" int flint_ssd_prepare(const float* raw, long long raw_stride, const f
   return check_launch("ssd_prepare");
 }
 
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_scan(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               Args&&... args) {
+  if (early) return launch_pdl(kernel, grid, block, smem, stream, static_cast<Args&&>(args)...);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 extern "C" int flint_recurrence_scan(const float* q, long long q_stride, const float* k, long long k_stride, const float* v,
                                      long long v_stride, const float* decay, int delta, const float* w1, const float* skip,
                                      const int* slot, const int* seq_start, int n_seq, float* state,
@@ -560,9 +579,13 @@ extern "C" int flint_recurrence_scan(const float* q, long long q_stride, const f
   auto lined = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   const bool vec = D % 4 == 0 && V % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && v_stride % 4 == 0 && lined(q) &&
                    lined(k) && lined(v) && (!delta || lined(decay));
+  // A walk over prompts starts as an ordinary dependent, on an empty chip, where its few blocks get an SM each: started
+  // early they land beside the blocks of the kernel before, several to an SM (a prompt of 2,048 tokens then ran half
+  // a millisecond longer a layer).  A batch of single tokens fills the chip anyway and starts early.
+  const bool early = seq_start == nullptr;
 #define SCAN(TPC, DELTA, VEC)                                                                                          \
-  launch_pdl(recurrence_scan_kernel<TPC, DELTA, VEC>, grid, block, smem, stream, q, q_stride, k, k_stride, v, v_stride, \
-             decay, w1, skip, slot, seq_start, state, state_stride, o, H, G, D, V, tb)
+  launch_scan(early, recurrence_scan_kernel<TPC, DELTA, VEC>, grid, block, smem, stream, q, q_stride, k, k_stride, v,   \
+              v_stride, decay, w1, skip, slot, seq_start, state, state_stride, o, H, G, D, V, tb)
 #define SCAN_T(TPC)                                                                                       \
   do {                                                                                                    \
     if (delta) { if (vec) SCAN(TPC, true, true); else SCAN(TPC, true, false); }                           \
@@ -604,7 +627,7 @@ extern "C" int flint_branch_mean(int n, const float* const* partials, const long
     bl.bias[b] = bias[b];
     bl.w[b] = w[b];
   }
-  launch_pdl(branch_mean_kernel, dim3((unsigned)T), dim3(W >= 1024 ? 256 : 128), 0, stream, bl, eps, out, W);
+  launch_pdl(branch_mean_kernel, dim3((unsigned)T), dim3(row_threads(W)), 0, stream, bl, eps, out, W);
   return check_launch("branch_mean");
 }
 
@@ -620,7 +643,7 @@ extern "C" int flint_post_norm(float* x, const float* partials, int n_partials, 
     cudaFuncSetAttribute(post_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
   }
   FLINT_DISPATCH_DTYPE(copy_dtype, TC,
-      launch_pdl(post_norm_kernel<TC>, dim3((unsigned)T), dim3(W >= 1024 ? 256 : 128), smem, stream, x, partials, n_partials,
+      launch_pdl(post_norm_kernel<TC>, dim3((unsigned)T), dim3(row_threads(W)), smem, stream, x, partials, n_partials,
                  partial_stride, bias, s, a, gamma, beta, eps, mode, (TC*)copy, W));
   return check_launch("post_norm");
 }
