@@ -194,6 +194,18 @@ def test_replay_matches_plain_in_mixed_batches_with_slots_and_pages_used_again(s
         assert max(max(g.pages.pool.served) for g in rp.model.cache.groups) >= 2
 
 
+@pytest.mark.parametrize("seed", [2, 23])
+def test_configurations_drawn_at_random_match_plain(seed, tmp_path):
+    """Sizes, constants and orders of layers that no other test has, whole, in twos and in a mixed batch."""
+    cfg, ranks = tiny.random_config(seed)
+    folder, w = tiny.write_model(tmp_path / "m", cfg, seed=seed, ranks=ranks)
+    reqs = traces.make_requests(cfg["vocab"], (1, 2, 9, 37), seed=seed)
+    plain = {rid: P.forward(cfg, w, t) for rid, t in reqs.items()}
+    for steps in (traces.whole(reqs), traces.portions(reqs, sizes=(2, 2, 1, 2, 3, 128)), traces.mixed(reqs, seed=3)):
+        out, _ = replay(folder, steps)
+        compare(out, steps, plain)
+
+
 def test_every_state_starts_from_zero_in_a_slot_that_was_used(setup):
     """One slot, three requests one after the other: each must see the state of a new sequence (the matrices of
     the recurrences and the convolutions' last inputs alike)."""

@@ -453,6 +453,24 @@ def test_replay_matches_plain_under_every_cut(setup, dtype):
             assert max(max(g.pages.pool.served) for g in rp.model.cache.groups) >= 2
 
 
+@pytest.mark.parametrize("seed", [2, 7, 23, 41])
+def test_configurations_drawn_at_random_match_plain_in_float32(seed, tmp_path):
+    """Sizes, constants and orders of layers that no other test has, whole and under three cuts."""
+    cfg, ranks = tiny.random_config(seed)
+    folder, w = tiny.write_model(tmp_path / "m", cfg, seed=seed, ranks=ranks)
+    reqs = traces.make_requests(cfg["vocab"], (1, 2, 9, 37, 70, 150), seed=seed)
+    plain = {rid: P.forward(cfg, w, t) for rid, t in reqs.items()}
+    cuts = {"whole": traces.whole, "tail": lambda r: traces.tail_decoded(r, tail=24),
+            "twos": lambda r: traces.portions(r, sizes=(2, 2, 1, 2, 3, 128)), "mixed": lambda r: traces.mixed(r, seed=3)}
+    for name, cut in cuts.items():
+        steps = cut(reqs)
+        out, _ = replay(folder, steps, "float32", page_size=16 if name == "mixed" else 64)
+        exp = traces.expected_rows(steps, plain)
+        assert set(out) == set(exp)
+        errs = torch.cat([rel_err(out[k], torch.stack(rows)) for k, rows in exp.items()])
+        assert float(errs.max()) < 1e-4, f"{name}: worst {float(errs.max()):.3g} for {cfg}"
+
+
 def test_a_cut_changes_float32_logits_by_rounding_only(setup):
     """The same request whole, in twos and token by token: the recurrences and the convolutions walk the tokens in
     the same order whatever the cut, so the logits agree far below the distance to the plain implementation."""

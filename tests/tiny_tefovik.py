@@ -139,3 +139,33 @@ def random_weights(cfg, seed=0, ranks=(3, 5)):
 
 def write_model(folder, cfg, seed=0, weights=None, ranks=(3, 5)):
     return _write_folder(folder, cfg, seed, weights if weights is not None else random_weights(cfg, seed, ranks))
+
+
+def random_config(seed):
+    """A configuration drawn at random: one to five layers in any order, with or without a feed-forward, head counts,
+    head sizes (also odd ones, 130 and 256 key dims, states of 7 to 256), rotated dims, runs of 1 to 1,000 positions or
+    none, one to five taps, norm parts and constants.  Returns (config, ranks of the delta rule's low-rank pairs)."""
+    import random
+    r = random.Random(1000 + seed)
+    layers = []
+    for _ in range(r.randint(1, 5)):
+        ff = r.choice([None, 16, 56, 96, 128])
+        if r.random() < 0.55:
+            kv = r.choice([1, 2, 3, 4])
+            d = r.choice([8, 10, 16, 32, 64, 48])
+            left = _left(kv * r.choice([1, 2, 3]), kv, d, r.choice([4, 10, 16, 32, 64, 18]), r.choice([0.1, 0.3, d ** -0.5]),
+                         r.randint(1, 5), r.choice([None, 1, 3, 16, 17, 64, 100, 200, 1000]), r.choice([0, d, d // 4 * 2, 2]),
+                         base=r.choice([100.0, 1e4, 5e5]))
+            g = r.choice([1, 2, 3])
+            right = _right(g * r.choice([1, 2]), g, r.choice([6, 20, 32, 40, 64, 128, 130, 256]),
+                           r.choice([6, 12, 32, 33, 48, 64]), r.randint(1, 5))
+            layers.append(_par(left, right, ff))
+        else:
+            G = r.choice([1, 2, 4])
+            H, V = G * r.choice([1, 2, 3]), r.choice([6, 10, 16, 32, 64])
+            parts = r.choice([n for n in (1, 2, 3, 4, H) if (H * V) % n == 0])
+            layers.append(_ssm(H, V, r.choice([7, 16, 32, 40, 48, 128, 144, 256]), G, parts, r.randint(1, 5), ff))
+    cfg = {"architecture": "Tefovik", "vocab": r.choice([83, 160, 301]), "width": r.choice([24, 40, 64, 72, 96, 128]),
+           "norm": {"eps": r.choice([1e-5, 1e-6])}, "postln_alpha": r.choice([1.0, 2.0, 3.5]),
+           "logit_softcap": r.choice([8.0, 15.0, 30.0]), "layers": layers}
+    return cfg, (r.choice([1, 3, 8]), r.choice([2, 5, 16]))
