@@ -28,12 +28,16 @@ from .pages import NO_PAGE, GroupPages
 class KVSpec:
     """What a mixer needs cached per token: ``num_kv_heads`` keys of ``head_dim`` numbers and as many values of
     ``value_dim`` numbers (default: as wide as the keys; 0: keys only).  ``window`` 0 means every key stays
-    reachable; otherwise only the last ``window`` positions, and the first ``keep_first`` of the sequence."""
+    reachable; otherwise only the last ``window`` positions, and the first ``keep_first`` of the sequence.
+    ``pool`` P > 0: beside every page the group keeps room for one mean key and one mean value per block of P
+    positions, ceil(page size / P) a page; block b of a request lies in slot b % n of the request's page b // n, a page
+    the request holds by the time the block is complete (so such a group keeps its pages: ``window`` stays 0)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
     value_dim: int | None = None
     keep_first: int = 0
+    pool: int = 0
 
     @property
     def value_width(self) -> int:
@@ -68,6 +72,16 @@ class GroupCache:
         self.keys = torch.zeros((len(self.calls), n, spec.num_kv_heads, P, spec.head_dim), dtype=dtype, device=device)
         self.values = torch.zeros((len(self.calls), n, spec.num_kv_heads, P, spec.value_width), dtype=dtype, device=device)
         self.block_table = torch.full((max_slots, max_pages_per_request), NO_PAGE, dtype=torch.int32, device=device)
+        # means of blocks of keys and values [call, page, kv_head, means a page, width]
+        self.pool_slots = -(-P // spec.pool) if spec.pool else 0
+        self.pool_keys = self.pool_values = None
+        if spec.pool:
+            if spec.window:
+                raise CacheError("a group that keeps block means keeps its pages (window must be 0)")
+            self.pool_keys = torch.zeros((len(self.calls), n, spec.num_kv_heads, self.pool_slots, spec.head_dim), dtype=dtype,
+                                         device=device)
+            self.pool_values = torch.zeros((len(self.calls), n, spec.num_kv_heads, self.pool_slots, spec.value_width),
+                                           dtype=dtype, device=device)
         # The copy to the device is asynchronous and may run long after it was asked for (behind a whole step
         # that is still running), while the bookkeeping goes on changing the host mirror for the next step:
         # the changed rows are therefore copied from a snapshot, two of which alternate.
@@ -98,18 +112,24 @@ class GroupCache:
 
     def view(self, call_index: int):
         i = self.calls.index(call_index)
-        return CacheView(self.keys[i], self.values[i], self.block_table, self.pages.page_size, self.spec)
+        return CacheView(self.keys[i], self.values[i], self.block_table, self.pages.page_size, self.spec,
+                         pool_k=self.pool_keys[i] if self.pool_keys is not None else None,
+                         pool_v=self.pool_values[i] if self.pool_values is not None else None, pool_slots=self.pool_slots)
 
 
 @dataclass
 class CacheView:
     """What a mixer call sees of the cache: its K pages [page, kv_head, P, head_dim], its V pages
-    [page, kv_head, P, value width] and its group's block table [slot, logical page]."""
+    [page, kv_head, P, value width] and its group's block table [slot, logical page]; for a group that keeps means
+    of blocks, those of keys and values [page, kv_head, ``pool_slots``, width]."""
     k: torch.Tensor
     v: torch.Tensor
     block_table: torch.Tensor
     page_size: int
     spec: KVSpec
+    pool_k: torch.Tensor | None = None
+    pool_v: torch.Tensor | None = None
+    pool_slots: int = 0
 
 
 class CacheManager:

@@ -41,6 +41,16 @@ class LayerCall:
 
 
 @dataclass(frozen=True)
+class PassInput:
+    """Before entry ``call`` of the run order the rows are mixed with the embedded rows again:
+    x <- W [x; x0] + b[row], with x0 the rows as the embedding left them, W = ``<pass_input_name>in`` [hidden, 2 hidden]
+    (x's columns first) and b = ``<pass_input_name>step`` [rows, hidden].  A model whose layers run several times in
+    a row (the same ``LayerSpec`` called again, each call with a cache of its own) opens every pass this way."""
+    call: int
+    row: int
+
+
+@dataclass(frozen=True)
 class ModelSpec:
     architecture: str
     vocab_size: int
@@ -75,3 +85,6 @@ class ModelSpec:
     depth_mix_name: str = "dwa"
     # logits <- c tanh(logits / c) (0: as they are)
     logit_softcap: float = 0.0
+    # Entries of the run order before which the rows are mixed with the embedded rows (``PassInput``).
+    pass_inputs: tuple = ()
+    pass_input_name: str = "loop."

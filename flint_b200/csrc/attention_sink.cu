@@ -102,6 +102,54 @@ __global__ void qkv_write_kernel(const float* __restrict__ qkv, int n_partials, 
   }
 }
 
+// ------------------------------------------------------------------------------------------- means of blocks of keys and values
+// A row whose position p ends a block of `pool` positions (p + 1 a multiple of pool) writes the block's mean key and
+// mean value, taken over the cache rows as they stand (so after norm and rotation, and in the cache's precision), in
+// float32 and in the order of the positions, into row b = (p + 1) / pool - 1 of the request's block means: slot
+// b % pool_slots of the request's page b / pool_slots, pool_slots = ceil(page_size / pool) means a page (that page
+// is one the request already holds: b / pool_slots <= (b pool + pool - 1) / page_size).  Whatever the cut of a
+// prompt, a block is written once, by the step that brings its last position, after that step's cache rows.
+template <typename TC>
+__global__ void pool_write_kernel(const TC* __restrict__ k_cache, const TC* __restrict__ v_cache, TC* __restrict__ pool_k,
+                                  TC* __restrict__ pool_v, const int* __restrict__ block_table, int max_pages,
+                                  int page_size, const int* __restrict__ pos, const int* __restrict__ slot, int nkv, int hd,
+                                  int vd, int pool, int pool_slots, int* __restrict__ status) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x, kvh = blockIdx.y, p = pos[t];
+  if ((p + 1) % pool) return;
+  const int b = (p + 1) / pool - 1, j0 = b * pool;
+  const int* bt = block_table + (size_t)slot[t] * max_pages;
+  const int home = b / pool_slots < max_pages ? bt[b / pool_slots] : -1;
+  if (home < 0) {
+    if (threadIdx.x == 0) atomicExch(status, 1);
+    return;
+  }
+  const size_t dst = ((size_t)home * nkv + kvh) * pool_slots + b % pool_slots;
+  const float share = 1.0f / (float)pool;
+  for (int d = threadIdx.x; d < hd + vd; d += blockDim.x) {
+    float sum = 0.f;
+    for (int j = j0; j <= p; ++j) {
+      const int page = bt[j / page_size];
+      if (page < 0) { atomicExch(status, 1); continue; }
+      const size_t at = ((size_t)page * nkv + kvh) * page_size + j % page_size;
+      sum += d < hd ? to_f32(k_cache[at * hd + d]) : to_f32(v_cache[at * vd + (d - hd)]);
+    }
+    if (d < hd) pool_k[dst * hd + d] = from_f32<TC>(sum * share);
+    else pool_v[dst * vd + (d - hd)] = from_f32<TC>(sum * share);
+  }
+}
+
+// Weights without a softmax (see the attention kernel): on, the cap of the scores (0: none), per query head the
+// distance penalty's two numbers and the bias (null: none).
+struct SigmoidWeights {
+  int on;
+  float cap;
+  const float* r1;
+  const float* r2;
+  const float* bias;
+};
+
 // ------------------------------------------------------------------------------------------- attention
 // DPL: value dims a lane holds (vd <= 32 DPL); the narrow forms keep fewer registers, so more blocks fit an SM and
 // hide each other's waits for their key rows.
@@ -111,7 +159,8 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
                       const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ pos,
                       const int* __restrict__ slot, TO* __restrict__ out, float* __restrict__ scratch, int T, int nq,
                       int nkv, int hd, int vd, int window, int keep_first, int run, const float* __restrict__ sinks, float scale,
-                      int split_keys, int n_splits, int g_chunks, const int* __restrict__ row_list) {
+                      int split_keys, int n_splits, int g_chunks, const int* __restrict__ row_list,
+                      const TC* __restrict__ pool_k, const TC* __restrict__ pool_v, int pool, int pool_slots, SigmoidWeights sw) {
   extern __shared__ float smem[];  // per warp: GC * hd floats of q
   pdl_launch();
   pdl_wait();
@@ -129,7 +178,9 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
   const int p = pos[t];
   // the first key of the stretch that ends at p: the window's start, or the start of p's run of `run` positions
   const int lo = run > 0 ? (p / run) * run : (window > 0 ? max(0, p + 1 - window) : 0);
-  const int n_first = min(keep_first, lo);              // kept keys below the window's start
+  // keys below the window's start: the kept first ones, or one mean key per block of `pool` positions that lies
+  // wholly below it (block b, positions b pool .. b pool + pool - 1, if b pool + pool - 1 <= p - window)
+  const int n_first = pool > 0 ? max(0, (p - window + 1) / pool) : min(keep_first, lo);
   const int total = n_first + (p + 1 - lo);             // seen keys, numbered 0 .. total - 1
   const int u_lo = split * split_keys, u_hi = min(total, u_lo + split_keys);
   const int* bt = block_table + (size_t)slot[t] * max_pages;
@@ -151,17 +202,25 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
 
   for (int u0 = u_lo; u0 < u_hi; u0 += 32) {
     const int u = u0 + lane;
-    long long row = -1;   // index of the key's row in [page, kv_head, P] units
+    long long row = -1;   // index of the key's row in [page, kv_head, P] units; -2 - (its row among the block means)
+    int dist = 0;         // how far behind the query the key lies
     if (u < u_hi) {
-      const int j = u < n_first ? u : lo + (u - n_first);
-      const int page = bt[j / page_size];
-      if (page >= 0) row = ((long long)page * nkv + kvh) * page_size + (j % page_size);
+      if (pool > 0 && u < n_first) {
+        const int page = bt[u / pool_slots];
+        if (page >= 0) row = -2 - (((long long)page * nkv + kvh) * pool_slots + (u % pool_slots));
+      } else {
+        const int j = u < n_first ? u : lo + (u - n_first);
+        const int page = bt[j / page_size];
+        if (page >= 0) row = ((long long)page * nkv + kvh) * page_size + (j % page_size);
+        dist = p - j;
+      }
     }
+    const bool have = row != -1;
     float s[GC];
 #pragma unroll
     for (int g = 0; g < GC; ++g) s[g] = 0.f;
-    if (row >= 0) {
-      const TC* kr = k_cache + row * hd;
+    if (have) {
+      const TC* kr = row >= 0 ? k_cache + row * hd : pool_k + (-2 - row) * hd;
       if (k_vec) {
 #pragma unroll 2
         for (int d = 0; d < hd; d += 8) {
@@ -184,17 +243,31 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
       }
     }
     float pr[GC];
+    if (sw.on) {
+      // no softmax: a key's weight is sigmoid(cap tanh(score / cap) - r1 ln(1 + r2 distance) + bias), not normalised
 #pragma unroll
-    for (int g = 0; g < GC; ++g) {
-      const float sg = row >= 0 ? s[g] : -INFINITY;
-      const float m_new = fmaxf(m[g], warp_max(sg));
-      const bool any = m_new > -INFINITY;
-      const float alpha = any ? expf(m[g] - m_new) : 1.f;
-      pr[g] = (any && row >= 0) ? expf(sg - m_new) : 0.f;
-      l[g] = l[g] * alpha + warp_sum(pr[g]);
-      m[g] = m_new;
+      for (int g = 0; g < GC; ++g) {
+        float z = s[g];
+        if (sw.cap > 0.f) z = sw.cap * tanhf(z / sw.cap);
+        if (g < ng) {
+          if (sw.r1) z -= sw.r1[h0 + g] * logf(1.0f + sw.r2[h0 + g] * (float)dist);
+          if (sw.bias) z += sw.bias[h0 + g];
+        }
+        pr[g] = have ? 1.0f / (1.0f + expf(-z)) : 0.f;
+      }
+    } else {
 #pragma unroll
-      for (int i = 0; i < DPL; ++i) acc[g][i] *= alpha;
+      for (int g = 0; g < GC; ++g) {
+        const float sg = have ? s[g] : -INFINITY;
+        const float m_new = fmaxf(m[g], warp_max(sg));
+        const bool any = m_new > -INFINITY;
+        const float alpha = any ? expf(m[g] - m_new) : 1.f;
+        pr[g] = (any && have) ? expf(sg - m_new) : 0.f;
+        l[g] = l[g] * alpha + warp_sum(pr[g]);
+        m[g] = m_new;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[g][i] *= alpha;
+      }
     }
     const int nk = min(32, u_hi - u0);
     constexpr int VU = 4;      // value rows in flight per lane
@@ -203,8 +276,8 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
 #pragma unroll
       for (int u = 0; u < VU; ++u) {
         const long long vrow = __shfl_sync(0xffffffffu, row, (jj0 + u) & 31);
-        const bool ok = jj0 + u < nk && vrow >= 0;
-        const TC* vr = v_cache + (ok ? vrow : 0) * vd;
+        const bool ok = jj0 + u < nk && vrow != -1;
+        const TC* vr = !ok ? v_cache : (vrow >= 0 ? v_cache + vrow * vd : pool_v + (-2 - vrow) * vd);
 #pragma unroll
         for (int i = 0; i < DPL; ++i) {
           const int d = lane + 32 * i;
@@ -232,7 +305,8 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
     for (int g = 0; g < GC; ++g)
       if (g < ng) {
         float scale_o = 1.f, sum = l[g];
-        if (sinks) {      // the sink joins the maximum and the sum
+        if (sw.on) sum = 1.f;          // the weights are used as they are
+        else if (sinks) {      // the sink joins the maximum and the sum
           const float sk = sinks[h0 + g], m_all = fmaxf(m[g], sk);
           scale_o = m[g] > -INFINITY ? expf(m[g] - m_all) : 0.f;
           sum = l[g] * scale_o + expf(sk - m_all);
@@ -266,12 +340,20 @@ sink_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
 // Merge the splits of one (row, head) and add the sink: out = sum_s e^(m_s - M) o_s / (sum_s e^(m_s - M) l_s + e^(sink - M)).
 template <typename TO>
 __global__ void sink_combine_kernel(const float* __restrict__ scratch, TO* __restrict__ out, int vd, int n_splits, int nq,
-                                    const float* __restrict__ sinks, const int* __restrict__ row_list) {
+                                    const float* __restrict__ sinks, const int* __restrict__ row_list, int plain_sum) {
   pdl_launch();
   pdl_wait();
   const size_t rh = blockIdx.x;   // (index of the row in this launch) * nq + head
   const size_t out_rh = row_list ? (size_t)row_list[rh / nq] * nq + rh % nq : rh;
   const float* base = scratch + rh * n_splits * (vd + 2);
+  if (plain_sum) {                // weights that are not normalised: the splits' sums add up, in a fixed order
+    for (int d = threadIdx.x; d < vd; d += blockDim.x) {
+      float o = 0.f;
+      for (int s = 0; s < n_splits; ++s) o += base[(size_t)s * (vd + 2) + d];
+      out[out_rh * vd + d] = from_f32<TO>(o);
+    }
+    return;
+  }
   const float sk = sinks ? sinks[rh % nq] : -INFINITY;
   float M = sk;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, base[(size_t)s * (vd + 2) + vd]);
@@ -549,13 +631,28 @@ extern "C" int flint_qkv_write(const float* qkv, int n_partials, long long parti
   return check_launch("qkv_write");
 }
 
+extern "C" int flint_pool_write(const void* k_cache, const void* v_cache, void* pool_k, void* pool_v, int cache_dtype,
+                                const int* block_table, int max_pages, int page_size, const int* pos, const int* slot,
+                                int T, int nkv, int hd, int vd, int pool, int pool_slots, int* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (pool < 1 || pool_slots < 1 || (long long)pool_slots * pool < page_size)
+    return fail("pool_write: %d means a page do not hold blocks of %d positions on pages of %d", pool_slots, pool, page_size);
+  FLINT_DISPATCH_DTYPE(cache_dtype, TC,
+      (launch_pdl(pool_write_kernel<TC>, dim3((unsigned)T, (unsigned)nkv), dim3(128), 0, stream, (const TC*)k_cache,
+                  (const TC*)v_cache, (TC*)pool_k, (TC*)pool_v, block_table, max_pages, page_size, pos, slot, nkv, hd, vd,
+                  pool, pool_slots, status)));
+  return check_launch("pool_write");
+}
+
 // `scratch` must hold T * nq * n_splits * (vd + 2) floats when n_splits > 1; split_keys * n_splits must cover the
 // most keys any row sees.  With a row list, T counts the listed rows and row_list[i] is the batch row of the i-th.
 extern "C" int flint_sink_attention(const void* q, int q_dtype, const void* k_cache, const void* v_cache, int cache_dtype,
                                     const int* block_table, int max_pages, int page_size, const int* pos,
                                     const int* slot, void* out, int T, int nq, int nkv, int hd, int vd, int window,
                                     int keep_first, int run, const float* sinks, float scale, int split_keys,
-                                    int n_splits, float* scratch, const int* row_list, cudaStream_t stream) {
+                                    int n_splits, float* scratch, const int* row_list, const void* pool_k,
+                                    const void* pool_v, int pool, int pool_slots, int sigmoid, float cap, const float* r1,
+                                    const float* r2, const float* w_bias, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd < 1 || vd < 1 || hd > 256 || vd > 32 * MAX_DPL)
     return fail("sink_attention: head sizes %d (keys) and %d (values) are not supported (1 to 256)", hd, vd);
@@ -564,6 +661,11 @@ extern "C" int flint_sink_attention(const void* q, int q_dtype, const void* k_ca
   if (n_splits > 1 && !scratch) return fail("sink_attention: splits need scratch memory");
   if (window < 0 || keep_first < 0 || run < 0 || (run > 0 && (window > 0 || keep_first > 0)))
     return fail("sink_attention: bad window (a run length excludes a window and kept first tokens)");
+  if (pool < 0 || (pool > 0 && (window < 1 || keep_first > 0 || run > 0 || !pool_k || !pool_v || pool_slots < 1)))
+    return fail("sink_attention: block means need a window, their storage, and no kept first tokens or runs");
+  if (sigmoid && (sinks || (r1 == nullptr) != (r2 == nullptr)))
+    return fail("sink_attention: weights without a softmax take no sink, and both numbers of the distance penalty or none");
+  const SigmoidWeights sw = {sigmoid ? 1 : 0, cap, r1, r2, w_bias};
   const int elem = cache_dtype == FLINT_F32 ? 4 : 2;
   if ((hd % 8) == 0 && (((uintptr_t)k_cache) & 15)) return fail("sink_attention: the key cache must start on 16 bytes");
   (void)elem;
@@ -576,7 +678,8 @@ extern "C" int flint_sink_attention(const void* q, int q_dtype, const void* k_ca
 #define LAUNCH_D(TQ, TC, DPL)                                                                                         \
   launch_pdl(sink_attention_kernel<TQ, TC, TQ, DPL>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream, (const TQ*)q, \
              (const TC*)k_cache, (const TC*)v_cache, block_table, max_pages, page_size, pos, slot, (TQ*)out, scratch, T, \
-             nq, nkv, hd, vd, window, keep_first, run, sinks, scale, split_keys, n_splits, g_chunks, row_list)
+             nq, nkv, hd, vd, window, keep_first, run, sinks, scale, split_keys, n_splits, g_chunks, row_list,           \
+             (const TC*)pool_k, (const TC*)pool_v, pool, pool_slots, sw)
 #define LAUNCH(TQ, TC)                                                     \
   do {                                                                     \
     if (vd <= 64) LAUNCH_D(TQ, TC, 2);                                     \
@@ -591,7 +694,7 @@ extern "C" int flint_sink_attention(const void* q, int q_dtype, const void* k_ca
   const int threads = vd >= 128 ? 128 : 64;
   FLINT_DISPATCH_DTYPE(q_dtype, TO,
       (launch_pdl(sink_combine_kernel<TO>, dim3((unsigned)((long long)T * nq)), dim3(threads), 0, stream,
-                  (const float*)scratch, (TO*)out, vd, n_splits, nq, sinks, row_list)));
+                  (const float*)scratch, (TO*)out, vd, n_splits, nq, sinks, row_list, sigmoid ? 1 : 0)));
   return check_launch("sink_combine");
 }
 

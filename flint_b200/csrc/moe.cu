@@ -405,6 +405,69 @@ extern "C" int flint_router_sigmoid(const float* x, const void* wr, int w_dtype,
   return check_launch("router_sigmoid");
 }
 
+// The grouped sigmoid router (select_sigmoid_grouped_by_warp) as a kernel of its own: a warp takes RT tokens, walks
+// the experts' weight rows once for all of them, then selects token by token.
+template <typename TW>
+__global__ void __launch_bounds__(128)
+router_sigmoid_grouped_kernel(const float* __restrict__ x, const TW* __restrict__ wr, const float* __restrict__ correction,
+                              int T, int H, int E, int top, int n_groups, int keep, int normalize, float out_scale,
+                              int* __restrict__ expert_ids, float* __restrict__ gates, float* __restrict__ logits_out) {
+  extern __shared__ float smem[];            // per warp: RT * E logits, then E choice scores
+  pdl_launch();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = (blockIdx.x * 4 + warp) * RT;
+  if (t0 >= T) return;
+  const int nt = min(RT, T - t0);
+  float* z = smem + warp * (RT + 1) * E;
+  float* c = z + RT * E;
+  for (int e = 0; e < E; ++e) {
+    float acc[RT];
+#pragma unroll
+    for (int r = 0; r < RT; ++r) acc[r] = 0.f;
+    const TW* w = wr + (size_t)e * H;
+    for (int d = lane; d < H; d += 32) {
+      const float wv = to_f32(w[d]);
+#pragma unroll
+      for (int r = 0; r < RT; ++r)
+        if (r < nt) acc[r] = fmaf(x[(size_t)(t0 + r) * H + d], wv, acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < RT; ++r) {
+      const float v = warp_sum(acc[r]);
+      if (lane == 0 && r < nt) z[r * E + e] = v;
+    }
+  }
+  __syncwarp();
+  for (int r = 0; r < nt; ++r) {
+    const int t = t0 + r;
+    float* zr = z + r * E;
+    if (logits_out)
+      for (int e = lane; e < E; e += 32) logits_out[(size_t)t * E + e] = zr[e];
+    __syncwarp();
+    select_sigmoid_grouped_by_warp(zr, c, correction, lane, E, top, n_groups, keep, normalize, out_scale,
+                                   expert_ids + (size_t)t * top, gates + (size_t)t * top);
+    __syncwarp();
+  }
+}
+
+extern "C" int flint_router_sigmoid_grouped(const float* x, const void* wr, int w_dtype, const float* correction, int E,
+                                            int top, int n_groups, int keep, int normalize, float out_scale,
+                                            int* expert_ids, float* gates, float* logits_out, int T, int H,
+                                            cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E < 1 || top < 1 || top > E || top > 32) return fail("router_sigmoid_grouped: %d of %d experts is not supported", top, E);
+  if (n_groups < 1 || n_groups > 64 || E % n_groups || keep < 1 || keep > n_groups || keep * (E / n_groups) < top)
+    return fail("router_sigmoid_grouped: %d of %d groups of %d experts cannot give %d a token", keep, n_groups, E, top);
+  const size_t smem = (size_t)4 * (RT + 1) * E * sizeof(float);
+  if (smem > 48 * 1024) return fail("router_sigmoid_grouped: too many experts (%d)", E);
+  const unsigned blocks = (unsigned)((T + 4 * RT - 1) / (4 * RT));
+  FLINT_DISPATCH_DTYPE(w_dtype, TW,
+      launch_pdl(router_sigmoid_grouped_kernel<TW>, dim3(blocks), dim3(128), smem, stream, x, (const TW*)wr, correction, T, H,
+                 E, top, n_groups, keep, normalize, out_scale, expert_ids, gates, logits_out));
+  return check_launch("router_sigmoid_grouped");
+}
+
 extern "C" int flint_moe_max_tiles(int n_assign, int E, int tile_rows) {
   return n_assign / tile_rows + (E < n_assign ? E : n_assign);
 }

@@ -794,16 +794,26 @@ class CudaOps:
         return keys, -(-span // keys)
 
     def sink_attention(self, q, cache, step, out, nq, nkv, hd, vd, window, keep_first, sinks, scale, splits=None,
-                       tiling=None, rows=None, chunk=0):
+                       tiling=None, rows=None, chunk=0, pool=0, sigmoid=None):
         """Every row over its request's cached keys [.., hd] and values [.., vd]: row at position p sees key j if
         j <= p and (p - j < window or j < keep_first) (window 0: all); ``sinks`` [nq] float32 (or None): a logit
         per query head that joins the softmax's denominator.  q [T, nq hd] -> out [T, nq vd].  ``tiling``: the step's
         rows cut into tiles of up to 64 rows (``engine.step.Tiling``): in bfloat16, with head sizes in multiples of
         16 up to 128, the tiles run on the tensor cores and only the rows in no tile row by row.  ``rows``: int32
         list of the batch rows to compute (default: all).  ``chunk`` c > 0 (instead of a window): the row sees key j
-        if j <= p and floor(j / c) = floor(p / c)."""
+        if j <= p and floor(j / c) = floor(p / c).  ``pool`` P > 0 (with a window): behind the window the row also sees
+        one mean key and value per block of P positions that lies wholly before it, from ``cache.pool_k`` /
+        ``cache.pool_v`` (written by ``pool_write``), in the same softmax.  ``sigmoid`` = (cap, r1, r2, bias) instead
+        of a softmax: key j weighs sigmoid(cap tanh(score / cap) - r1_h ln(1 + r2_h (p - j)) + bias_h), not normalised
+        (cap 0: no cap; r1, r2, bias float32 [nq] or None)."""
         _check(q, "q", dims=2)
         _check(out, "out", q.dtype, 2)
+        cap, r1, r2, w_bias = sigmoid if sigmoid is not None else (0.0, None, None, None)
+        for name, t in (("r1", r1), ("r2", r2), ("bias", w_bias)):
+            if t is not None and (t.dtype != torch.float32 or t.numel() != nq):
+                raise KernelError(f"sink_attention: {name} must be float32 [{nq}]")
+        if pool and (not window or cache.pool_k is None or cache.pool_slots * pool < cache.page_size):
+            raise KernelError("sink_attention: block means need a window and the cache's storage for them")
         T = q.shape[0]
         P = cache.page_size
         if chunk and (window or keep_first):
@@ -816,7 +826,7 @@ class CudaOps:
             _check(sinks, "sinks", torch.float32, 1)
             if sinks.numel() != nq:
                 raise KernelError(f"sink_attention: sinks must have {nq} entries")
-        if (tiling is not None and tiling.n_tiles > 0 and rows is None and splits is None
+        if (tiling is not None and tiling.n_tiles > 0 and rows is None and splits is None and not pool and sigmoid is None
                 and self.sink_attention_tiles_ok(q.dtype, cache.k.dtype, hd, vd)):
             _check(tiling.tiles, "tiles", torch.int32)
             self._run("attention_sink", "flint_sink_attention_tiles", _ptr(q), _ptr(cache.k), _ptr(cache.v),
@@ -830,6 +840,8 @@ class CudaOps:
             _check(rows, "rows", torch.int32, 1)
             T = rows.numel()
         span = min(step.max_kv_len, window + keep_first) if window else step.max_kv_len
+        if pool:
+            span = min(step.max_kv_len, window + step.max_kv_len // pool)
         if chunk:
             span = min(span, chunk)
         keys, n = splits if splits is not None else self.sink_attention_plan(T, nq, nkv, span)
@@ -840,7 +852,24 @@ class CudaOps:
                   c_int(_code(cache.k.dtype)), _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(P),
                   _ptr(step.pos), _ptr(step.slot), _ptr(out), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(vd),
                   c_int(window), c_int(keep_first), c_int(chunk), _ptr(sinks), c_float(scale), c_int(keys), c_int(n),
-                  _ptr(scratch), _ptr(rows))
+                  _ptr(scratch), _ptr(rows), _ptr(cache.pool_k if pool else None), _ptr(cache.pool_v if pool else None),
+                  c_int(pool), c_int(cache.pool_slots if pool else 0), c_int(1 if sigmoid is not None else 0), c_float(cap),
+                  _ptr(r1), _ptr(r2), _ptr(w_bias))
+
+    def pool_write(self, cache, step, nkv, hd, vd, pool):
+        """Every row of the step whose position ends a block of ``pool`` positions writes the block's mean key and
+        value (over the cache rows as they stand, float32 sums in the order of the positions) into ``cache.pool_k`` /
+        ``cache.pool_v`` [page, kv head, means a page, width]: block b of a request lies in slot b % n of the request's
+        page b // n, n = ``cache.pool_slots``."""
+        if cache.pool_k is None or cache.pool_slots * pool < cache.page_size:
+            raise KernelError("pool_write: the cache has no storage for block means of this size")
+        P, E = cache.page_size, cache.pool_slots
+        if tuple(cache.pool_k.shape[1:]) != (nkv, E, hd) or tuple(cache.pool_v.shape[1:]) != (nkv, E, vd):
+            raise KernelError("pool_write: the block means' storage does not match the head counts")
+        self._run("attention_sink", "flint_pool_write", _ptr(cache.k), _ptr(cache.v), _ptr(cache.pool_k), _ptr(cache.pool_v),
+                  c_int(_code(cache.k.dtype)), _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(P),
+                  _ptr(step.pos), _ptr(step.slot), c_int(step.n_tokens), c_int(nkv), c_int(hd), c_int(vd), c_int(pool),
+                  c_int(E), _ptr(step.status))
 
     @staticmethod
     def sink_attention_tiles_ok(q_dtype, cache_dtype, hd, vd):
@@ -1076,19 +1105,25 @@ class CudaOps:
         self._run("recurrent", "flint_cast_rows", _ptr(x), _ptr(out), c_int(_code(out.dtype)), c_longlong(x.numel()))
 
     def qk_norm_write(self, y, q_norm, k_norm, eps, pos, slot, cos, sin, rot, style, v_cos, v_sin, v_style, q_out, cache,
-                      nq, nkv, hd, vd, status):
+                      nq, nkv, hd, vd, status, whole=False, v_from_k=False, q_temp=None):
         """y [T, (nq + nkv) hd + nkv vd] float32 (q | k | v): every q and k head is divided by its root mean square
         and scaled by q_norm / k_norm [hd] (both None: no norm), its leading ``rot`` dims rotate by the row's
         position; every value head rotates over all vd dims with tables of its own (None: not at all).  q goes to
-        q_out [T, nq hd], keys and values into the row's cache page."""
+        q_out [T, nq hd], keys and values into the row's cache page.  ``whole``: q is divided by one root mean square
+        over all its heads and scaled by q_norm [nq hd], k likewise with k_norm [nkv hd].  ``v_from_k``: the values are
+        the keys as projected, before norm and rotation (vd = hd; y has no value columns).  ``q_temp`` = (coef, every):
+        q at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1)."""
         _check(y, "y", torch.float32, 2, contiguous=False)
         T = y.shape[0]
-        if y.stride(1) != 1 or y.shape[1] < (nq + nkv) * hd + nkv * vd:
+        if y.stride(1) != 1 or y.shape[1] < (nq + nkv) * hd + (0 if v_from_k else nkv * vd):
             raise KernelError("qk_norm_write: the rows' width does not match the head counts")
+        if v_from_k and vd != hd:
+            raise KernelError("qk_norm_write: values that are the keys need vd = hd")
+        qt_coef, qt_every = (float(q_temp[0]), int(q_temp[1])) if q_temp is not None else (0.0, 1)
         _check(q_out, "q_out", dims=2)
         if tuple(q_out.shape) != (T, nq * hd):
             raise KernelError(f"qk_norm_write: q_out must be [{T}, {nq * hd}]")
-        for name, t, n in (("q_norm", q_norm, hd), ("k_norm", k_norm, hd)):
+        for name, t, n in (("q_norm", q_norm, nq * hd if whole else hd), ("k_norm", k_norm, nkv * hd if whole else hd)):
             if t is not None and (t.dtype != torch.float32 or t.numel() != n):
                 raise KernelError(f"qk_norm_write: {name} must be float32 [{n}]")
         if rot and (cos is None or cos.shape[1] * 2 != rot):
@@ -1103,11 +1138,13 @@ class CudaOps:
                   _ptr(pos), _ptr(slot), _ptr(cos), _ptr(sin), c_int(rot), c_int(1 if style == "interleaved" else 0),
                   _ptr(v_cos), _ptr(v_sin), c_int(1 if v_style == "interleaved" else 0), _ptr(q_out),
                   c_int(_code(q_out.dtype)), _ptr(k), _ptr(v), c_int(_code(k.dtype)), _ptr(bt), c_int(bt.shape[1]), c_int(P),
-                  c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(vd), _ptr(status))
+                  c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(vd), c_int(1 if whole else 0),
+                  c_int(1 if v_from_k else 0), c_float(qt_coef), c_int(qt_every), _ptr(status))
 
     def head_finish(self, attn, pos, v_cos, v_sin, v_style, gate, out, nq, vd):
         """attn [T, nq vd]: every head's sum is turned back by the row's position (tables None: not at all) and
-        multiplied by sigmoid(gate[t, head]) (gate a [T, nq] float32 view, or None)."""
+        multiplied by sigmoid(gate[t, head]) (gate a [T, nq] float32 view, or None), or, with a gate [T, nq vd], number
+        by number by sigmoid(gate[t, head, d])."""
         _check(attn, "attn", dims=2)
         _check(out, "out", attn.dtype, 2)
         T = attn.shape[0]
@@ -1115,11 +1152,72 @@ class CudaOps:
             raise KernelError("head_finish: shapes do not match")
         if gate is not None:
             _check(gate, "gate", torch.float32, 2, contiguous=False)
-            if tuple(gate.shape) != (T, nq) or gate.stride(1) != 1:
-                raise KernelError("head_finish: the gates must be [rows, heads]")
+            if tuple(gate.shape) not in ((T, nq), (T, nq * vd)) or gate.stride(1) != 1:
+                raise KernelError("head_finish: the gates must be [rows, heads] or [rows, heads x value dims]")
         self._run("recurrent", "flint_head_finish", _ptr(attn), c_int(_code(attn.dtype)), _ptr(pos), _ptr(v_cos), _ptr(v_sin),
                   c_int(1 if v_style == "interleaved" else 0), _ptr(gate),
-                  c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out), c_int(T), c_int(nq), c_int(vd))
+                  c_longlong(gate.stride(0) if gate is not None else 0),
+                  c_int(1 if gate is not None and gate.shape[1] == nq * vd and vd > 1 else 0), _ptr(out), c_int(T), c_int(nq),
+                  c_int(vd))
+
+    def sum_norm_add(self, dst, branches=(), scales=(), expert_rows=None, gamma=None, eps=0.0, accumulate=True):
+        """r[t] = sum_b scales[b] * y_b[t] + sum_j gates[t, j] * y[row_of[t, j]] with y_b the sum of branch b's partial
+        sums plus its bias (``branches`` [(partials [S, T, W] float32, bias [W] or None)], up to four) and
+        ``expert_rows`` = (y [*, W], row_of [T, k] int32, gates [T, k]) or None; with ``gamma`` [W]:
+        r <- r / sqrt(mean(r^2) + eps) * gamma; then dst [T, W] float32 += r (``accumulate``) or dst = r."""
+        _check(dst, "dst", torch.float32, 2)
+        T, W = dst.shape
+        n = len(branches)
+        if n > 4 or len(scales) != n:
+            raise KernelError("sum_norm_add: up to four branches, a scale each")
+        ptrs, strides, counts, biases = [], [], [], []
+        for part, bias in branches:
+            _check(part, "partials", torch.float32, 3)
+            if tuple(part.shape[1:]) != (T, W):
+                raise KernelError("sum_norm_add: shapes do not match")
+            if bias is not None and (bias.dtype != torch.float32 or bias.numel() != W):
+                raise KernelError("sum_norm_add: a bias must be float32 of the rows' width")
+            ptrs.append(part.data_ptr())
+            strides.append(part.stride(0))
+            counts.append(part.shape[0])
+            biases.append(bias.data_ptr() if bias is not None else 0)
+        y = row_of = gates = None
+        k = 0
+        if expert_rows is not None:
+            y, row_of, gates = expert_rows
+            _check(y, "y", torch.float32, 2)
+            _check(row_of, "row_of", torch.int32, 2)
+            _check(gates, "gates", torch.float32, 2)
+            k = row_of.shape[1]
+            if y.shape[1] != W or tuple(row_of.shape) != (T, k) or tuple(gates.shape) != (T, k):
+                raise KernelError("sum_norm_add: the expert rows' shapes do not match")
+        if gamma is not None and (gamma.dtype != torch.float32 or gamma.numel() != W):
+            raise KernelError("sum_norm_add: gamma must be float32 of the rows' width")
+        m = max(n, 1)
+        arr = lambda ctype, vals: (ctype * m)(*vals)
+        self._run("recurrent", "flint_sum_norm_add", c_int(n), arr(c_void_p, ptrs), arr(c_longlong, strides), arr(c_int, counts),
+                  arr(c_void_p, biases), arr(c_float, [float(x) for x in scales]), _ptr(y), _ptr(row_of), _ptr(gates), c_int(k),
+                  _ptr(gamma), c_float(eps), _ptr(dst), c_int(1 if accumulate else 0), c_int(T), c_int(W))
+
+    def retention_prepare(self, proj, pos, cos, sin, rot, style, decay_h, dt_value, qk, decay, dt, H, D):
+        """proj [T, >= 2 H D] float32 (q | k, H heads of D dims; rows may be strided): the leading ``rot`` dims of
+        every head turn by the row's position into qk [T, 2 H D]; decay [T, H] <- decay_h [H] and dt [T, H] <- dt_value
+        on every row (what the recurrence kernel takes per token)."""
+        _check(proj, "proj", torch.float32, 2, contiguous=False)
+        T = proj.shape[0]
+        if proj.stride(1) != 1 or proj.shape[1] < 2 * H * D:
+            raise KernelError("retention_prepare: the rows do not hold q and k")
+        for name, t, shape in (("qk", qk, (T, 2 * H * D)), ("decay", decay, (T, H)), ("dt", dt, (T, H))):
+            _check(t, name, torch.float32, 2)
+            if tuple(t.shape) != shape:
+                raise KernelError(f"retention_prepare: {name} must be {shape}")
+        if decay_h.dtype != torch.float32 or decay_h.numel() != H:
+            raise KernelError("retention_prepare: one float32 decay per head")
+        if rot and (cos is None or cos.shape[1] * 2 != rot):
+            raise KernelError("retention_prepare: table width must be rot/2")
+        self._run("recurrent", "flint_retention_prepare", _ptr(proj), c_longlong(proj.stride(0)), _ptr(pos), _ptr(cos),
+                  _ptr(sin), c_int(rot), c_int(1 if style == "interleaved" else 0), _ptr(decay_h), c_float(dt_value), _ptr(qk),
+                  _ptr(decay), _ptr(dt), c_int(T), c_int(H), c_int(D))
 
     # ------------------------------------------------------------------ attention over a cached latent
     def head_products(self, x, w, out):
@@ -1322,6 +1420,28 @@ class CudaOps:
                 raise KernelError(f"router: logits must be [{T}, {E + X}]")
         self._run("moe", "flint_router_sigmoid", _ptr(x), _ptr(wr), c_int(_code(wr.dtype)), c_int(E), c_int(X), c_int(top),
                   _ptr(expert_ids), _ptr(scores), _ptr(weights), _ptr(logits_out), c_int(T), c_int(H))
+
+    def router_sigmoid_grouped(self, x, wr, correction, top, n_groups, keep, normalize, scale, expert_ids, gates,
+                               logits_out=None):
+        """Scores sigmoid(x wr^T) in float32; choice scores add ``correction`` [E] (or None); a group of neighbouring
+        experts scores as the sum of its two largest choice scores, only the ``keep`` best of ``n_groups`` groups may be
+        chosen from, the ``top`` largest choice scores are (the lower index among equals); gates [T, top]: the chosen
+        experts' scores, over their sum (+ 1e-20) if ``normalize``, times ``scale``."""
+        _check(x, "x", torch.float32, 2)
+        _check(wr, "router weight", dims=2)
+        _check(expert_ids, "expert_ids", torch.int32, 2)
+        _check(gates, "gates", torch.float32, 2)
+        T, H = x.shape
+        E = wr.shape[0]
+        if wr.shape[1] != H or tuple(expert_ids.shape) != (T, top) or tuple(gates.shape) != (T, top):
+            raise KernelError("router_sigmoid_grouped: shapes do not match")
+        if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E):
+            raise KernelError("router_sigmoid_grouped: the correction must be float32, one per expert")
+        if logits_out is not None:
+            _check(logits_out, "logits_out", torch.float32, 2)
+        self._run("moe", "flint_router_sigmoid_grouped", _ptr(x), _ptr(wr), c_int(_code(wr.dtype)), _ptr(correction), c_int(E),
+                  c_int(top), c_int(n_groups), c_int(keep), c_int(1 if normalize else 0), c_float(scale), _ptr(expert_ids),
+                  _ptr(gates), _ptr(logits_out), c_int(T), c_int(H))
 
     def _plan_buffers(self, expert_ids, n_experts, tile_rows):
         _check(expert_ids, "expert_ids", torch.int32, 2)

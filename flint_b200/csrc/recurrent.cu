@@ -313,6 +313,91 @@ __global__ void gated_norm_kernel(const float* __restrict__ o, const float* __re
   }
 }
 
+// ------------------------------------------------------------------------------------------- weighted sums of branches, normed, added
+struct SumList {
+  const float* partials[4];
+  long long stride[4];       // between partial sums
+  int n_partials[4];
+  const float* bias[4];
+  float scale[4];
+  int n;
+  const float* y;            // rows of chosen experts [*, W] (or null), the places of a token's rows and their weights
+  const int* row_of;
+  const float* gates;
+  int k;
+};
+
+// r[t] = sum_b scale_b * y_b[t] + sum_j gates[t, j] * y[row_of[t, j]], y_b the sum of branch b's partial sums (+ bias);
+// with gamma: r <- r / sqrt(mean(r^2) + eps) * gamma; then dst[t] += r (accumulate) or dst[t] = r.
+__global__ void sum_norm_add_kernel(SumList sl, const float* __restrict__ gamma, float eps, float* __restrict__ dst,
+                                    int accumulate, int W) {
+  __shared__ float red[32];
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x;
+  auto value = [&](int c) {
+    float r = 0.f;
+    for (int b = 0; b < sl.n; ++b) {
+      float x = 0.f;
+      for (int z = 0; z < sl.n_partials[b]; ++z) x += sl.partials[b][(size_t)z * sl.stride[b] + (size_t)t * W + c];
+      if (sl.bias[b]) x += sl.bias[b][c];
+      r = fmaf(sl.scale[b], x, r);
+    }
+    for (int j = 0; j < sl.k; ++j)
+      r = fmaf(sl.gates[(size_t)t * sl.k + j], sl.y[(size_t)sl.row_of[(size_t)t * sl.k + j] * W + c], r);
+    return r;
+  };
+  float inv = 1.f;
+  if (gamma) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      const float x = value(c);
+      ss = fmaf(x, x, ss);
+    }
+    ss = block_sum(ss, red);
+    inv = 1.0f / sqrtf(ss / (float)W + eps);
+  }
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float r = value(c) * inv;
+    if (gamma) r *= gamma[c];
+    float* d = dst + (size_t)t * W + c;
+    *d = accumulate ? *d + r : r;
+  }
+}
+
+// ------------------------------------------------------------------------------------------- retention: rotated q and k, constant decays
+// proj [T, >= 2 H D] float32 (q | k of H heads of D dims): the leading `rot` dims of every head turn by the row's
+// position into qk [T, 2 H D]; decay [T, H] gets the head's fixed decay and dt [T, H] the constant that scales what is
+// written into the state (the recurrence kernel takes both per token).
+__global__ void retention_prepare_kernel(const float* __restrict__ proj, long long stride, const int* __restrict__ pos,
+                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
+                                         int interleaved, const float* __restrict__ decay_h, float dt_value,
+                                         float* __restrict__ qk, float* __restrict__ decay, float* __restrict__ dt, int H,
+                                         int D) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x, p = pos[t], half = rot / 2, n = 2 * H * D;
+  const float* row = proj + (size_t)t * stride;
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    const int d = e % D;
+    float x = row[e];
+    if (d < rot) {
+      int i, partner;
+      bool first;
+      if (interleaved) { i = d >> 1; first = !(d & 1); partner = first ? e + 1 : e - 1; }
+      else { i = d < half ? d : d - half; first = d < half; partner = first ? e + half : e - half; }
+      const float z = row[partner];
+      const float c = cos_t[(size_t)p * half + i], s = sin_t[(size_t)p * half + i];
+      x = first ? x * c - z * s : x * c + z * s;
+    }
+    qk[(size_t)t * n + e] = x;
+  }
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    decay[(size_t)t * H + h] = decay_h[h];
+    dt[(size_t)t * H + h] = dt_value;
+  }
+}
+
 // ------------------------------------------------------------------------------------------- mean of normed branches
 struct BranchList {
   const float* partials[4];
@@ -439,7 +524,9 @@ __global__ void qk_norm_write_kernel(const float* __restrict__ y, long long y_st
                                      const float* __restrict__ vcos, const float* __restrict__ vsin, int v_interleaved,
                                      TQ* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache,
                                      const int* __restrict__ block_table, int max_pages, int page_size, int nq, int nkv,
-                                     int hd, int vd, int* __restrict__ status) {
+                                     int hd, int vd, int whole, int v_from_k, float qt_coef, int qt_every,
+                                     int* __restrict__ status) {
+  __shared__ float part[2][32];
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -447,17 +534,40 @@ __global__ void qk_norm_write_kernel(const float* __restrict__ y, long long y_st
   const int page = lp < max_pages ? block_table[(size_t)slot[t] * max_pages + lp] : -1;
   if (page < 0 && threadIdx.x == 0) atomicExch(status, 1);
   const float* row = y + (size_t)t * y_stride;
+  // a temperature on the queries that grows with the position: 1 + coef ln(floor((p + 1) / every) + 1)
+  const float q_temp = qt_coef != 0.f ? 1.0f + qt_coef * logf(floorf((float)(p + 1) / (float)qt_every) + 1.0f) : 1.0f;
+  float inv_whole[2] = {1.f, 1.f};
+  if (whole && qw) {          // one root mean square over all query heads, one over all key heads
+    float sq = 0.f, sk = 0.f;
+    for (int e = threadIdx.x; e < nq * hd; e += blockDim.x) sq = fmaf(row[e], row[e], sq);
+    for (int e = threadIdx.x; e < nkv * hd; e += blockDim.x) sk = fmaf(row[(size_t)nq * hd + e], row[(size_t)nq * hd + e], sk);
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if (lane == 0) { part[0][warp] = sq; part[1][warp] = sk; }
+    __syncthreads();
+    sq = sk = 0.f;
+    for (int i = 0; i < nw; ++i) { sq += part[0][i]; sk += part[1][i]; }      // the same order in every thread
+    inv_whole[0] = 1.0f / sqrtf(sq / (float)(nq * hd) + eps);
+    inv_whole[1] = 1.0f / sqrtf(sk / (float)(nkv * hd) + eps);
+  }
   for (int head = warp; head < nq + 2 * nkv; head += nw) {
     const bool is_v = head >= nq + nkv;
     const int n = is_v ? vd : hd;
-    const float* src = is_v ? row + (size_t)(nq + nkv) * hd + (size_t)(head - nq - nkv) * vd : row + (size_t)head * hd;
+    // values that are the keys as projected come from the key's columns (vd = hd), before norm and rotation
+    const float* src = is_v ? (v_from_k ? row + (size_t)(head - nkv) * hd
+                                        : row + (size_t)(nq + nkv) * hd + (size_t)(head - nq - nkv) * vd)
+                            : row + (size_t)head * hd;
     const float* w = is_v ? nullptr : (head < nq ? qw : kw);
     float inv = 1.f;
-    if (w) {
+    if (w && whole) {
+      inv = inv_whole[head < nq ? 0 : 1];
+      w += (size_t)(head < nq ? head : head - nq) * hd;       // a scale per column of the projection
+    } else if (w) {
       float ss = 0.f;
       for (int d = lane; d < n; d += 32) ss = fmaf(src[d], src[d], ss);
       inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + eps);
     }
+    if (head < nq) inv *= q_temp;
     const float* ct = is_v ? vcos : cos_t;
     const float* st = is_v ? vsin : sin_t;
     const int r = is_v ? (vcos ? vd : 0) : rot, half = r / 2, il = is_v ? v_interleaved : interleaved;
@@ -487,7 +597,7 @@ __global__ void qk_norm_write_kernel(const float* __restrict__ y, long long y_st
 template <typename TA>
 __global__ void head_finish_kernel(const TA* __restrict__ attn, const int* __restrict__ pos, const float* __restrict__ vcos,
                                    const float* __restrict__ vsin, int interleaved, const float* __restrict__ gate,
-                                   long long gate_stride, TA* __restrict__ out, int T, int nq, int vd) {
+                                   long long gate_stride, int gate_each, TA* __restrict__ out, int T, int nq, int vd) {
   pdl_launch();
   pdl_wait();
   const int half = vd / 2;
@@ -503,9 +613,12 @@ __global__ void head_finish_kernel(const TA* __restrict__ attn, const int* __res
     u = u2;
     v = v2;
   }
-  const float g = gate ? sigmoidf_(gate[(size_t)t * gate_stride + head]) : 1.f;
-  out[base + a] = from_f32<TA>(u * g);
-  out[base + b] = from_f32<TA>(v * g);
+  // a gate per head, or one per number of every head
+  const float* gr = gate + (size_t)t * gate_stride;
+  const float ga = !gate ? 1.f : sigmoidf_(gate_each ? gr[(size_t)head * vd + a] : gr[head]);
+  const float gb = !gate ? 1.f : (gate_each ? sigmoidf_(gr[(size_t)head * vd + b]) : ga);
+  out[base + a] = from_f32<TA>(u * ga);
+  out[base + b] = from_f32<TA>(v * gb);
 }
 
 }  // namespace
@@ -613,6 +726,38 @@ extern "C" int flint_gated_norm(const float* o, const float* gate, long long gat
   return check_launch("gated_norm");
 }
 
+extern "C" int flint_sum_norm_add(int n, const float* const* partials, const long long* strides, const int* n_partials,
+                                  const float* const* bias, const float* scales, const float* y, const int* row_of,
+                                  const float* gates, int k, const float* gamma, float eps, float* dst, int accumulate,
+                                  int T, int W, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (n < 0 || n > 4) return fail("sum_norm_add: %d branches are not supported (up to 4)", n);
+  if (k < 0 || (k > 0 && (!y || !row_of || !gates))) return fail("sum_norm_add: expert rows need their places and weights");
+  if (n == 0 && k == 0) return fail("sum_norm_add: nothing to add");
+  SumList sl = {};
+  sl.n = n;
+  for (int b = 0; b < n; ++b) {
+    sl.partials[b] = partials[b];
+    sl.stride[b] = strides[b];
+    sl.n_partials[b] = n_partials[b];
+    sl.bias[b] = bias[b];
+    sl.scale[b] = scales[b];
+  }
+  sl.y = y; sl.row_of = row_of; sl.gates = gates; sl.k = k;
+  launch_pdl(sum_norm_add_kernel, dim3((unsigned)T), dim3(row_threads(W)), 0, stream, sl, gamma, eps, dst, accumulate, W);
+  return check_launch("sum_norm_add");
+}
+
+extern "C" int flint_retention_prepare(const float* proj, long long stride, const int* pos, const float* cos_t,
+                                       const float* sin_t, int rot, int interleaved, const float* decay_h, float dt_value,
+                                       float* qk, float* decay, float* dt, int T, int H, int D, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (rot < 0 || rot > D || rot % 2) return fail("retention_prepare: %d rotating dims do not fit heads of %d", rot, D);
+  launch_pdl(retention_prepare_kernel, dim3((unsigned)T), dim3(2 * H * D >= 1024 ? 256 : 128), 0, stream, proj, stride, pos,
+             cos_t, sin_t, rot, interleaved, decay_h, dt_value, qk, decay, dt, H, D);
+  return check_launch("retention_prepare");
+}
+
 extern "C" int flint_branch_mean(int n, const float* const* partials, const long long* strides, const int* n_partials,
                                  const float* const* bias, const float* const* w, float eps, float* out, int T, int W,
                                  cudaStream_t stream) {
@@ -676,27 +821,29 @@ extern "C" int flint_qk_norm_write(const float* y, long long y_stride, const flo
                                    const int* pos, const int* slot, const float* cos_t, const float* sin_t, int rot,
                                    int interleaved, const float* vcos, const float* vsin, int v_interleaved, void* q_out,
                                    int q_dtype, void* k_cache, void* v_cache, int cache_dtype, const int* block_table,
-                                   int max_pages, int page_size, int T, int nq, int nkv, int hd, int vd, int* status,
-                                   cudaStream_t stream) {
+                                   int max_pages, int page_size, int T, int nq, int nkv, int hd, int vd, int whole, int v_from_k,
+                                   float qt_coef, int qt_every, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (rot < 0 || rot > hd || rot % 2 || (vcos && vd % 2)) return fail("qk_norm_write: bad rotation sizes");
+  if (v_from_k && vd != hd) return fail("qk_norm_write: values that are the keys need vd = hd");
+  if (qt_coef != 0.f && qt_every < 1) return fail("qk_norm_write: the query temperature's period must be positive");
   if ((qw == nullptr) != (kw == nullptr)) return fail("qk_norm_write: q and k are normed together or not at all");
   FLINT_DISPATCH_DTYPE(q_dtype, TQ, FLINT_DISPATCH_DTYPE(cache_dtype, TC,
       launch_pdl(qk_norm_write_kernel<TQ, TC>, dim3((unsigned)T), dim3(256), 0, stream, y, y_stride, qw, kw, eps, pos, slot,
                  cos_t, sin_t, rot, interleaved, vcos, vsin, v_interleaved, (TQ*)q_out, (TC*)k_cache, (TC*)v_cache,
-                 block_table, max_pages, page_size, nq, nkv, hd, vd, status)));
+                 block_table, max_pages, page_size, nq, nkv, hd, vd, whole, v_from_k, qt_coef, qt_every, status)));
   return check_launch("qk_norm_write");
 }
 
 extern "C" int flint_head_finish(const void* attn, int dtype, const int* pos, const float* vcos, const float* vsin,
-                                 int interleaved, const float* gate, long long gate_stride, void* out, int T, int nq, int vd,
-                                 cudaStream_t stream) {
+                                 int interleaved, const float* gate, long long gate_stride, int gate_each, void* out, int T,
+                                 int nq, int vd, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (vd % 2) return fail("head_finish: value heads of %d dims cannot rotate in pairs", vd);
   const long long n = (long long)T * nq * (vd / 2);
   FLINT_DISPATCH_DTYPE(dtype, TA,
       launch_pdl(head_finish_kernel<TA>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const TA*)attn, pos, vcos,
-                 vsin, interleaved, gate, gate_stride, (TA*)out, T, nq, vd));
+                 vsin, interleaved, gate, gate_stride, gate_each, (TA*)out, T, nq, vd));
   return check_launch("head_finish");
 }
 

@@ -129,4 +129,79 @@ __device__ __forceinline__ void select_sigmoid_by_warp(float* s, int lane, int E
   for (int e = lane; e < extra; e += 32) weights[top + e] = s[E + e];
 }
 
+// The choice of a sigmoid router limited to groups, by one warp, from float32 logits in shared memory: scores
+// s = sigmoid(logit); choice scores c = s + correction (a learned offset per expert, or none); the E experts form
+// n_groups equal groups of neighbours and a group scores as the sum of its two largest choice scores (of its one,
+// if it has one member); only members of the `keep` best groups may be chosen (the others count as minus infinity:
+// choice scores may be negative); the `top` largest choice scores of those are chosen (the lower index among equals).
+// gates: the chosen experts' s, divided by their sum (+ 1e-20) if `normalize`, times out_scale.  `s` holds the logits
+// on entry and the scores afterwards; `c` is scratch for E floats in shared memory.
+__device__ __forceinline__ void select_sigmoid_grouped_by_warp(float* s, float* c, const float* __restrict__ correction,
+                                                               int lane, int E, int top, int n_groups, int keep,
+                                                               int normalize, float out_scale, int* ids, float* gates) {
+  for (int e = lane; e < E; e += 32) {
+    const float v = 1.0f / (1.0f + expf(-s[e]));
+    s[e] = v;
+    c[e] = correction ? v + correction[e] : v;
+  }
+  __syncwarp();
+  auto best_of_warp = [&](float& val, int& idx) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, val, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > val || (ov == val && oi < idx)) { val = ov; idx = oi; }
+    }
+  };
+  const int per = E / n_groups;
+  if (keep < n_groups) {
+    float gs[2];                                  // the scores of groups lane and lane + 32
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int g = lane + 32 * k;
+      gs[k] = -INFINITY;
+      if (g < n_groups) {
+        float a = -INFINITY, b = -INFINITY;       // the two largest of the group
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+          const float v = c[e];
+          if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+        }
+        gs[k] = per > 1 ? a + b : a;
+      }
+    }
+    unsigned long long kept = 0ull;
+    for (int r = 0; r < keep; ++r) {
+      float val = gs[0];
+      int idx = lane < n_groups ? lane : 0x7fffffff;
+      if (lane + 32 < n_groups && gs[1] > val) { val = gs[1]; idx = lane + 32; }
+      best_of_warp(val, idx);
+      kept |= 1ull << idx;
+      if ((idx & 31) == lane) gs[idx >> 5] = -INFINITY;
+    }
+    __syncwarp();
+    for (int e = lane; e < E; e += 32)
+      if (!((kept >> (e / per)) & 1ull)) c[e] = -INFINITY;
+    __syncwarp();
+  }
+  float my_val = 0.f, sum = 0.f;
+  int my_sel = 0;
+  for (int r = 0; r < top; ++r) {
+    float val = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (c[e] > val) { val = c[e]; idx = e; }
+    best_of_warp(val, idx);
+    const float sv = idx < E ? s[idx] : 0.f;
+    if (lane == r) { my_val = sv; my_sel = idx < E ? idx : 0; }
+    sum += sv;
+    __syncwarp();
+    if (lane == 0 && idx < E) c[idx] = -INFINITY;      // taken
+    __syncwarp();
+  }
+  if (lane < top) {
+    ids[lane] = my_sel;
+    gates[lane] = (normalize ? my_val / (sum + 1e-20f) : my_val) * out_scale;
+  }
+}
+
 }  // namespace flint

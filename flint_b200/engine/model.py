@@ -97,6 +97,10 @@ def expected_tensors(spec: ModelSpec, layers, final_norm, embed_position=None, e
         raise ConfigError("depth mix: a layer that is called twice cannot store one set of weights per call")
     for i, name in enumerate(names):
         exp[name] = WeightSpec((i + 2,), role="vector", init="gamma")
+    if spec.pass_inputs:
+        exp[spec.pass_input_name + "in"] = WeightSpec((spec.hidden_size, 2 * spec.hidden_size))
+        exp[spec.pass_input_name + "step"] = WeightSpec((max(p.row for p in spec.pass_inputs) + 1, spec.hidden_size),
+                                                        role="vector")
     if embed_position is not None:
         for name, ws in embed_position.weights().items():
             exp[spec.embed_position_name + name] = ws
@@ -162,6 +166,15 @@ class Model:
         if self.embed_norm is not None:
             self.embed_norm.load({n: tensors[spec.embed_norm_name + n] for n in self.embed_norm.weights()})
         self.depth_weights = [tensors[n] for n in depth_mix_names(spec)]
+        # x <- W [x; x0] + b[row] before some calls: the two halves of W's columns as matrices of their own
+        self.pass_inputs = {}
+        if spec.pass_inputs:
+            w_in, w_step, W = tensors[spec.pass_input_name + "in"], tensors[spec.pass_input_name + "step"], spec.hidden_size
+            self.pass_w = (w_in[:, :W].contiguous(), w_in[:, W:].contiguous())
+            for p in spec.pass_inputs:
+                if not 0 <= p.call < len(spec.order) or p.call in self.pass_inputs:
+                    raise ConfigError(f"pass input: call {p.call} is not an entry of the run order, or named twice")
+                self.pass_inputs[p.call] = w_step[p.row].contiguous()
         if self.embed_position is not None:
             self.embed_position.load({n: tensors[spec.embed_position_name + n] for n in self.embed_position.weights()})
         for part, prefix in self.embed_additions:
@@ -333,7 +346,21 @@ class Model:
         elif history is not None:
             history[0].copy_(h)
         carry = None     # an addition to h that a layer left for the next norm to apply
+        x0 = None        # the embedded rows in the type the pass inputs' product reads
+        if self.pass_inputs:
+            wdt = self.pass_w[0].dtype
+            x0 = torch.empty((T, spec.hidden_size), dtype=wdt, device=self.device)
+            ops.cast_rows(h, x0)
         for i, call in enumerate(self.order):
+            if i in self.pass_inputs:         # h <- W [h; x0] + b: two products into new rows, the residual sum in float32
+                if carry is not None:
+                    ops.apply_pending(h, carry)
+                    carry = None
+                hx = torch.empty_like(x0)
+                ops.cast_rows(h, hx)
+                h = torch.empty_like(h)
+                ops.gemm(hx, self.pass_w[0], h, bias=self.pass_inputs[i])
+                ops.gemm(x0, self.pass_w[1], h, accumulate=True)
             layer = self.layers[call.layer]
             owner = i if call.cache_of is None else call.cache_of
             carry = layer.block.forward(h, step, self.cache.view(owner), self.cache.state_of(i),

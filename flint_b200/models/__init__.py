@@ -1,2 +1,2 @@
 """Architectures.  Importing this package registers the built-in ones."""
-from . import gepadra, phimoe, puledra, tefovik  # noqa: F401
+from . import dumizen, gepadra, phimoe, puledra, tefovik  # noqa: F401

@@ -50,7 +50,18 @@ class Attention(Mixer):
     [head_dim], before they rotate), value_position (a PartSpec of a rotary encoding over all value dims: the
     value of position j is cached turned by j, and every head's sum is turned back by its query's position),
     head_gate (every head's output times sigmoid(W x), one number a head, tensor ``gate_proj.weight`` [num_heads,
-    hidden])."""
+    hidden]).
+
+    And: pool (P > 0, with a window: behind the window a position also sees one mean key and one mean value for every
+    block of P positions that lies wholly before the window, block b if b P + P - 1 <= p - window; the means are taken
+    over the cached rows and join the same softmax; such a layer keeps its pages), qk_norm "whole" (q is divided by one
+    root mean square over all its heads and scaled by ``q_norm.weight`` [num_heads head_dim], k likewise), values_from_keys
+    (no value projection: the values are the keys as projected, before norm and rotation), unit_sink (one is added
+    to the softmax's denominator: a sink whose logit is 0), out_gate (the heads' outputs times sigmoid(W x) number by
+    number, tensor ``gate_proj.weight`` [num_heads value_dim, hidden]), q_temp (coef, every: q at position p times
+    1 + coef ln(floor((p + 1) / every) + 1)), weights "sigmoid" (no softmax: key j weighs sigmoid(z + b_h), not
+    normalised, with z the score, capped as softcap tanh(z / softcap) if ``softcap`` > 0, less r1_h ln(1 + r2_h (p - j))
+    with ``distance_bias``; tensors ``r1``, ``r2``, and with ``weight_bias`` ``pb``, one number a query head)."""
 
     graph_safe = True
     returns_pending = True       # the output projection always leaves as partial sums; the rows given are not touched
@@ -78,6 +89,27 @@ class Attention(Mixer):
             raise ConfigError("attention: a window and runs of a fixed length cannot be combined")
         self.taps = int(p.get("conv_taps", 0) or 0)
         self.qk_norm = bool(p.get("qk_norm", False))
+        self.qk_whole = p.get("qk_norm") == "whole"
+        self.pool = int(p.get("pool", 0) or 0)
+        if self.pool and (not self.window or self.keep_first or self.chunk):
+            raise ConfigError("attention: means of blocks need a window, and exclude kept first tokens and runs")
+        self.values_from_keys = bool(p.get("values_from_keys", False))
+        if self.values_from_keys and self.vd != self.hd:
+            raise ConfigError("attention: values that are the keys have the keys' size")
+        self.unit_sink = bool(p.get("unit_sink", False))
+        self.out_gate = bool(p.get("out_gate", False))
+        self.q_temp = tuple(p["q_temp"]) if p.get("q_temp") is not None else None
+        self.weights_rule = p.get("weights", "softmax")
+        if self.weights_rule not in ("softmax", "sigmoid"):
+            raise ConfigError(f"attention: weights must be 'softmax' or 'sigmoid', got {self.weights_rule!r}")
+        self.softcap = float(p.get("softcap", 0.0) or 0.0)
+        self.distance_bias, self.weight_bias = bool(p.get("distance_bias", False)), bool(p.get("weight_bias", False))
+        if self.weights_rule == "sigmoid" and (self.sinks or self.unit_sink):
+            raise ConfigError("attention: weights without a softmax take no sink")
+        if self.weights_rule != "sigmoid" and (self.softcap or self.distance_bias or self.weight_bias):
+            raise ConfigError("attention: a cap, a distance penalty and a bias of the weights belong to weights 'sigmoid'")
+        if self.sinks and self.unit_sink:
+            raise ConfigError("attention: a learned sink and a unit sink exclude each other")
         self.qk_eps = float(p.get("qk_norm_eps", 1e-6))
         self.head_gate = bool(p.get("head_gate", False))
         self.value_position = (shared_position_encoding(p["value_position"], ctx)
@@ -85,12 +117,16 @@ class Attention(Mixer):
         if self.value_position is not None and self.value_position.rotary_dim != self.vd:
             raise ConfigError("attention: the values' rotation must cover all value dims")
         # q, k and v take a longer way from the projection to the cache, and the heads' sums one to the output
-        self.reworked = bool(self.taps or self.qk_norm or self.head_gate or self.value_position is not None)
+        self.reworked = bool(self.taps or self.qk_norm or self.head_gate or self.value_position is not None or self.pool
+                             or self.values_from_keys or self.out_gate or self.q_temp is not None
+                             or self.weights_rule == "sigmoid")
+        if self.head_gate and self.out_gate:
+            raise ConfigError("attention: a gate per head and a gate per number exclude each other")
         if self.reworked and self.value_mix:
             raise ConfigError("attention: blended values cannot be combined with a convolution, q/k norms, rotated "
                               "values or a gate per head")
-        self.general = bool(self.vd != self.hd or self.keep_first or self.sinks or self.value_mix or self.chunk
-                            or self.reworked)
+        self.general = bool(self.vd != self.hd or self.keep_first or self.sinks or self.unit_sink or self.value_mix
+                            or self.chunk or self.reworked)
         if self.general:
             if max(self.hd, self.vd) > 256 or min(self.hd, self.vd) < 1:
                 raise ConfigError(f"head sizes {self.hd} (keys) and {self.vd} (values) are not supported (1 to 256)")
@@ -111,6 +147,9 @@ class Attention(Mixer):
              "v_proj.weight": mat(nkv * vd, H), "o_proj.weight": mat(H, nq * vd)}
         if self.qkv_bias:
             w.update({"q_proj.bias": vec(nq * hd), "k_proj.bias": vec(nkv * hd), "v_proj.bias": vec(nkv * vd)})
+        if self.values_from_keys:
+            w.pop("v_proj.weight")
+            w.pop("v_proj.bias", None)
         if self.out_bias:
             w["o_proj.bias"] = vec(H)
         if self.sinks:
@@ -121,34 +160,48 @@ class Attention(Mixer):
             for n, rows in (("q", nq * hd), ("k", nkv * hd), ("v", nkv * vd)):
                 w[f"{n}_conv.weight"] = WeightSpec((rows, self.taps), role="vector", std=0.3)
         if self.qk_norm:
-            w.update({"q_norm.weight": vec(hd, init="gamma"), "k_norm.weight": vec(hd, init="gamma")})
+            w.update({"q_norm.weight": vec(nq * hd if self.qk_whole else hd, init="gamma"),
+                      "k_norm.weight": vec(nkv * hd if self.qk_whole else hd, init="gamma")})
         if self.head_gate:
             w["gate_proj.weight"] = mat(nq, H)
+        if self.out_gate:
+            w["gate_proj.weight"] = mat(nq * vd, H)
+        if self.distance_bias:
+            w.update({"r1": vec(nq), "r2": vec(nq, init="gamma")})
+        if self.weight_bias:
+            w["pb"] = vec(nq)
         return w
 
     def fused(self):
+        if self.values_from_keys:
+            return {}
         f = {"qkv_proj.weight": ["q_proj.weight", "k_proj.weight", "v_proj.weight"]}
         if self.qkv_bias:
             f["qkv_proj.bias"] = ["q_proj.bias", "k_proj.bias", "v_proj.bias"]
         return f
 
     def load(self, t):
-        dt = matmul_dtype(t["q_proj.weight"], t["k_proj.weight"], t["v_proj.weight"])
-        # one product gives q, k, v and, with a gate per head, its logits
-        pieces = [t["q_proj.weight"], t["k_proj.weight"], t["v_proj.weight"]] + ([t["gate_proj.weight"]] if self.head_gate else [])
+        qkv_names = ["q_proj.weight", "k_proj.weight"] + ([] if self.values_from_keys else ["v_proj.weight"])
+        gated = self.head_gate or self.out_gate
+        dt = matmul_dtype(*(t[n] for n in qkv_names), *([t["gate_proj.weight"]] if gated else []))
+        # one product gives q, k, v and, with a gate, its logits
+        pieces = [t[n] for n in qkv_names] + ([t["gate_proj.weight"]] if gated else [])
         self.w_qkv = torch.cat([w.to(dt) for w in pieces], 0)
         self.w_conv = (torch.cat([t["q_conv.weight"], t["k_conv.weight"], t["v_conv.weight"]], 0).contiguous()
                        if self.taps else None)
         self.q_norm, self.k_norm = t.get("q_norm.weight"), t.get("k_norm.weight")
         self.v_cos, self.v_sin = self.value_position.tables() if self.value_position is not None else (None, None)
-        self.b_qkv = (torch.cat([t["q_proj.bias"], t["k_proj.bias"], t["v_proj.bias"]], 0).contiguous()
+        self.b_qkv = (torch.cat([t[n.replace("weight", "bias")] for n in qkv_names], 0).contiguous()
                       if self.qkv_bias else None)
         # the same for a projection that also gives the gates' logits (which have no bias)
-        self.b_qkv_all = (torch.cat([self.b_qkv, self.b_qkv.new_zeros(self.nq)]) if self.qkv_bias and self.head_gate
-                          else self.b_qkv)
+        self.b_qkv_all = (torch.cat([self.b_qkv, self.b_qkv.new_zeros(t["gate_proj.weight"].shape[0])])
+                          if self.qkv_bias and gated else self.b_qkv)
         self.w_o = t["o_proj.weight"]
         self.b_o = t.get("o_proj.bias")
         self.sink = t.get("sinks")
+        if self.unit_sink:           # a sink whose logit is 0: one more in the denominator
+            self.sink = torch.zeros(self.nq, dtype=torch.float32, device=self.ctx.device)
+        self.sigmoid = ((self.softcap, t.get("r1"), t.get("r2"), t.get("pb")) if self.weights_rule == "sigmoid" else None)
         # read once, when the tensors arrive: the kernels take the blend weight as a launch parameter
         self.blend = float(t["value_mix"]) if self.value_mix == "blend" else 0.0
         if self.position is not None:
@@ -160,6 +213,8 @@ class Attention(Mixer):
         return (self.w_qkv.dtype,)
 
     def cache_spec(self):
+        if self.pool:            # the pages stay: the means of a page's blocks live beside it
+            return KVSpec(self.nkv, self.hd, 0, value_dim=None if self.vd == self.hd else self.vd, pool=self.pool)
         if self.general:
             return KVSpec(self.nkv, self.hd, self.window, value_dim=None if self.vd == self.hd else self.vd,
                           keep_first=self.keep_first)
@@ -174,7 +229,8 @@ class Attention(Mixer):
         if not self.general:
             return self.NEEDS
         ok = getattr(self.ops, "sink_attention_tiles_ok", None)
-        tiles = ok is not None and ok(self.ctx.act_dtype, self.ctx.act_dtype, self.hd, self.vd)
+        tiles = (ok is not None and ok(self.ctx.act_dtype, self.ctx.act_dtype, self.hd, self.vd)
+                 and not self.pool and self.weights_rule != "sigmoid")
         return self.NEEDS_GENERAL if tiles else None
 
     def plan_step(self, step, captured):
@@ -213,7 +269,7 @@ class Attention(Mixer):
         ops, nq, nkv, hd, vd = self.ops, self.nq, self.nkv, self.hd, self.vd
         T, dev = xin.shape[0], xin.device
         act = self.ctx.act_dtype if self.w_qkv.dtype == torch.bfloat16 else torch.float32
-        W = (nq + nkv) * hd + nkv * vd
+        W = (nq + nkv) * hd + (0 if self.values_from_keys else nkv * vd)
         proj = torch.empty((T, self.w_qkv.shape[0]), dtype=torch.float32, device=dev)
         ops.gemm(xin, self.w_qkv, proj, bias=self.b_qkv_all)
         if self.taps:
@@ -224,20 +280,25 @@ class Attention(Mixer):
         else:
             y = proj[:, :W]
         q = torch.empty((T, nq * hd), dtype=act, device=dev)
+        extra = {k: v for k, v in (("whole", self.qk_whole), ("v_from_k", self.values_from_keys), ("q_temp", self.q_temp))
+                 if v}
         ops.qk_norm_write(y, self.q_norm, self.k_norm, self.qk_eps, step.pos, step.slot, self.cos, self.sin, self.rot,
                           self.rot_style, self.v_cos, self.v_sin,
                           self.value_position.style if self.value_position is not None else "half", q, cache, nq, nkv, hd,
-                          vd, step.status)
+                          vd, step.status, **extra)
+        if self.pool:       # the blocks that this step completes get their mean key and value
+            ops.pool_write(cache, step, nkv, hd, vd, self.pool)
         attn = torch.empty((T, nq * vd), dtype=act, device=dev)
         needs = self.step_needs()
+        more = {k: v for k, v in (("pool", self.pool), ("sigmoid", self.sigmoid)) if v}
         ops.sink_attention(q, cache, step, attn, nq, nkv, hd, vd, self.window, self.keep_first, self.sink, self.scale,
                            tiling=step.tiling(needs) if needs is not None and q.dtype == torch.bfloat16 else None,
-                           chunk=self.chunk)
-        if self.head_gate or self.value_position is not None:
+                           chunk=self.chunk, **more)
+        if self.head_gate or self.out_gate or self.value_position is not None:
             out = torch.empty_like(attn)
             ops.head_finish(attn, step.pos, self.v_cos, self.v_sin,
                             self.value_position.style if self.value_position is not None else "half",
-                            proj[:, W:] if self.head_gate else None, out, nq, vd)
+                            proj[:, W:] if self.head_gate or self.out_gate else None, out, nq, vd)
             attn = out
         return Pending(partials=ops.gemm_partials(attn, self.w_o), bias=self.b_o)
 

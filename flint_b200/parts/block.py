@@ -6,6 +6,8 @@
 ``parallel_two_norms``: h += mixer(norm1(h)) + ffn(norm2(h)), both of the same h.
 ``postnorm``: h <- norm1(a h + s1 * mixer(h)); h <- norm2(a h + s2 * ffn(h)): the parts read the rows themselves and
 the norms come after the sums (a and the scales s are the norms' ``residual_scale`` and ``branch_scale``).
+``sandwich``: h += norm1b(mixer(norm1(h))); h += norm2b(ffn(norm2(h))): a norm before and one after each part, the
+second applied to what the part adds (RMS norms; the second half only with a feed-forward).
 An arrangement only orders parts; it does not know what they are.
 """
 from __future__ import annotations
@@ -131,6 +133,44 @@ class ParallelTwoNormsBlock(Block):
         mixed = mixer.forward(x, residual, step, cache, state, writes_cache)
         fed = ffn.forward(y, residual, step, routed=routed) if routed is not None else ffn.forward(y, residual, step)
         return merge_pending(mixer, residual, mixed, fed)
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """h += n1b(mixer(n1(h))); h += n2b(ffn(n2(h))).  What a part adds (partial sums of its last product, or its
+    chosen experts' rows with their weights) is summed, divided by its root mean square, scaled and added into the rows
+    by one kernel; nothing is left pending for the next layer."""
+    roles = ("norm1", "mixer", "norm1b")
+
+    def _run(self, part, norm_after, residual, call):
+        """residual += norm_after(what the part adds).  A part that says ``returns_pending`` hands back what it adds
+        (partial sums with a bias, or expert rows with their weights); any other adds into a zeroed buffer."""
+        if norm_after.mode != "rms":
+            raise ConfigError("block 'sandwich': the norms after the parts are RMS norms")
+        pend = call(None) if getattr(part, "returns_pending", False) else branch_of(part, residual, call)
+        branches = [(pend.partials, pend.bias)] if pend.partials is not None else []
+        rows = (pend.y, pend.row_of, pend.gates) if pend.y is not None else None
+        part.ops.sum_norm_add(residual, branches, [1.0] * len(branches), expert_rows=rows, gamma=norm_after.gamma,
+                              eps=norm_after.eps)
+
+    def forward(self, residual, step, cache, state, writes_cache=True, carry=None):
+        p = self.parts
+        mixer, ffn = p["mixer"], p.get("ffn")
+        x, _ = run_norm(p["norm1"], residual, mixer.input_dtypes(), carry)
+        self._run(mixer, p["norm1b"], residual, lambda rows: mixer.forward(x, rows, step, cache, state, writes_cache))
+        if ffn is None:
+            return None
+        if "norm2" not in p or "norm2b" not in p:
+            raise ConfigError("block 'sandwich': a feed-forward needs its two norms (norm2, norm2b)")
+        request = ffn.router_request(residual.shape[0]) if hasattr(ffn, "router_request") else None
+        routed_by_norm = request is not None and p["norm2"].supports_router
+        if routed_by_norm and step.record is not None and getattr(request, "logits", 0) is None:
+            request.logits = request.weight.new_empty((residual.shape[0], request.weight.shape[0]), dtype=torch.float32)
+        want = ffn.input_dtypes_when_routed() if routed_by_norm else ffn.input_dtypes()
+        y, routed = run_norm(p["norm2"], residual, want, None, request if routed_by_norm else None)
+        self._run(ffn, p["norm2b"], residual,
+                  lambda rows: ffn.forward(y, rows, step, routed=routed) if routed is not None else ffn.forward(y, rows, step))
+        return None
 
 
 def rows_in(part_ops, residual, step, dtypes):

@@ -1,7 +1,10 @@
 """A mixer made of several mixers side by side: all read the same rows, and the result is the mean of their
-outputs, each first divided by its root mean square over the width and scaled by a weight of its own.
+outputs, each first divided by its root mean square over the width and scaled by a weight of its own,
 
     out = (1 / n) sum_b  w_b * y_b / sqrt(mean(y_b^2) + eps)
+
+or, with ``combine: "weighted"``, the plain weighted sum  out = sum_b scale_b y_b  with one constant a branch
+(``scales``) and no stored weights.
 
 Each branch is any registered mixer, built from its own ``PartSpec``; its tensors live under ``<name>.`` and its
 weight w_b is ``<name>.out``.  A branch may own a paged cache (at most one branch of a mixer may) and fixed-size
@@ -22,14 +25,21 @@ from .block import branch_of
 
 @MIXERS.register("branches")
 class Branches(Mixer):
-    """params: hidden_size, eps, branches: ((name, PartSpec), ...).  tensors: every branch's own under ``<name>.``,
-    and ``<name>.out`` [hidden]."""
+    """params: hidden_size, eps, branches: ((name, PartSpec), ...), combine ("rms_mean", the default, or "weighted"
+    with ``scales``, one number a branch).  tensors: every branch's own under ``<name>.``, and for the mean
+    ``<name>.out`` [hidden]."""
 
     returns_pending = True
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
-        self.hidden, self.eps = int(params["hidden_size"]), float(params["eps"])
+        self.hidden, self.eps = int(params["hidden_size"]), float(params.get("eps", 0.0))
+        self.combine = params.get("combine", "rms_mean")
+        if self.combine not in ("rms_mean", "weighted"):
+            raise ConfigError(f"branches: combine must be 'rms_mean' or 'weighted', got {self.combine!r}")
+        self.scales = tuple(float(x) for x in params.get("scales", ()))
+        if self.combine == "weighted" and len(self.scales) != len(params["branches"]):
+            raise ConfigError("branches: a weighted sum needs one scale a branch")
         self.branches = [(name, MIXERS.get(ps.kind)(ps.params, ctx)) for name, ps in params["branches"]]
         if not 1 <= len(self.branches) <= 4:
             raise ConfigError(f"branches: {len(self.branches)} branches are not supported (1 to 4)")
@@ -43,7 +53,8 @@ class Branches(Mixer):
         for name, m in self.branches:
             for k, ws in m.weights().items():
                 w[f"{name}.{k}"] = ws
-            w[f"{name}.out"] = vec(self.hidden, init="gamma")
+            if self.combine == "rms_mean":
+                w[f"{name}.out"] = vec(self.hidden, init="gamma")
         return w
 
     def fused(self):
@@ -53,7 +64,8 @@ class Branches(Mixer):
         self.out_w = []
         for name, m in self.branches:
             m.load({k: t[f"{name}.{k}"] for k in m.weights() if f"{name}.{k}" in t})
-            self.out_w.append(t[f"{name}.out"])
+            if self.combine == "rms_mean":
+                self.out_w.append(t[f"{name}.out"])
 
     def input_dtypes(self):
         return tuple({dt for _, m in self.branches for dt in m.input_dtypes()})
@@ -95,5 +107,8 @@ class Branches(Mixer):
                                   lambda rows, m=m, c=c, st=st: m.forward(x, rows, step, c, st, writes_cache)))
         T = outs[0].partials.shape[1]
         out = torch.empty((1, T, self.hidden), dtype=torch.float32, device=outs[0].partials.device)
-        self.ops.branch_mean([(o.partials, o.bias) for o in outs], self.out_w, self.eps, out[0])
+        if self.combine == "weighted":
+            self.ops.sum_norm_add(out[0], [(o.partials, o.bias) for o in outs], self.scales, accumulate=False)
+        else:
+            self.ops.branch_mean([(o.partials, o.bias) for o in outs], self.out_w, self.eps, out[0])
         return Pending(partials=out)

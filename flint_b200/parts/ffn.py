@@ -13,7 +13,7 @@ import torch
 
 from ..errors import ConfigError
 from ..registry import FEED_FORWARDS
-from .base import FeedForward, Pending, RouterRequest, mat, matmul_dtype
+from .base import FeedForward, Pending, RouterRequest, mat, matmul_dtype, vec
 
 
 @FEED_FORWARDS.register("gated_mlp")
@@ -260,11 +260,21 @@ class SigmoidTopKMoE(FeedForward):
     the experts' pending rows.  (No counterpart in the reference, whose feed-forward is dense:
     crates/thuban_model/src/ops/mlp.rs:24-79.)
 
+    With ``weighting: "output"`` the chosen experts' OUTPUTS are weighted instead, and the choice may follow the
+    grouped rule: choice scores s + ``correction`` (a stored offset per expert); the experts form ``groups`` equal
+    groups of neighbours, a group scores as the sum of its two largest choice scores, only members of the
+    ``keep_groups`` best groups can be chosen, the ``top`` largest choice scores among them are; the weights are the
+    chosen experts' s, over their sum (+ 1e-20) if ``normalize``, times ``router_scale``.  ``shared_gate: False``: the
+    shared expert is added as it is (no gate tensor).
+
     params: hidden_size, intermediate_size, num_experts, top, shared_intermediate_size (0: none), act ("gelu",
-    the erf form, or "gelu_pytorch_tanh", "silu").
-    tensors: router [E, H]; e{i}.up [I, H], e{i}.down [H, I]; shared.up [Is, H], shared.down [H, Is], shared.sg [1, H]."""
+    the erf form, or "gelu_pytorch_tanh", "silu", "relu2"); weighting ("input", the default, or "output"), groups,
+    keep_groups, correction, normalize, router_scale, shared_gate (default true).
+    tensors: router [E, H]; e{i}.up [I, H], e{i}.down [H, I]; shared.up [Is, H], shared.down [H, Is], shared.sg [1, H];
+    correction [E]."""
 
     graph_safe = True
+    returns_pending = True        # the rows given are never touched: what the experts add goes back as a Pending
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -277,8 +287,26 @@ class SigmoidTopKMoE(FeedForward):
             raise ConfigError(f"num_experts {self.E} is not supported (1..256)")
         if not 1 <= self.top <= min(self.E, 16):
             raise ConfigError(f"{self.top} experts a token of {self.E} is not supported (1..16)")
-        if self.act not in ("gelu", "gelu_pytorch_tanh", "silu"):
+        self.weighting = p.get("weighting", "input")
+        if self.weighting not in ("input", "output"):
+            raise ConfigError(f"sigmoid_topk_moe: weighting must be 'input' or 'output', got {self.weighting!r}")
+        self.groups, self.keep = int(p.get("groups", 1)), int(p.get("keep_groups", 1))
+        self.correction = bool(p.get("correction", False))
+        self.normalize = bool(p.get("normalize", False))
+        self.router_scale = float(p.get("router_scale", 1.0))
+        self.shared_gate = bool(p.get("shared_gate", True))
+        if self.weighting == "input" and (self.groups > 1 or self.correction or self.normalize or self.router_scale != 1.0
+                                          or not self.shared_gate):
+            raise ConfigError("sigmoid_topk_moe: groups, a correction, normalised or scaled weights and an ungated shared "
+                              "expert go with weighting 'output'")
+        if self.groups < 1 or self.groups > 64 or self.E % self.groups:
+            raise ConfigError(f"{self.E} experts do not form {self.groups} equal groups (up to 64)")
+        if not 1 <= self.keep <= self.groups or self.keep * (self.E // self.groups) < self.top:
+            raise ConfigError(f"{self.keep} of {self.groups} groups cannot give {self.top} experts a token")
+        if self.act not in ("gelu", "gelu_pytorch_tanh", "silu", "relu2"):
             raise ConfigError(f"sigmoid_topk_moe: unknown activation {self.act!r}")
+        if self.weighting == "input" and self.act == "relu2":
+            raise ConfigError("sigmoid_topk_moe: act 'relu2' goes with weighting 'output'")
 
     def weights(self):
         w = {"router": mat(self.E, self.hidden)}
@@ -286,15 +314,19 @@ class SigmoidTopKMoE(FeedForward):
             w[f"e{e}.up"] = mat(self.inter, self.hidden)
             w[f"e{e}.down"] = mat(self.hidden, self.inter)
         if self.shared:
-            w.update({"shared.up": mat(self.shared, self.hidden), "shared.down": mat(self.hidden, self.shared),
-                      "shared.sg": mat(1, self.hidden)})
+            w.update({"shared.up": mat(self.shared, self.hidden), "shared.down": mat(self.hidden, self.shared)})
+            if self.shared_gate:
+                w["shared.sg"] = mat(1, self.hidden)
+        if self.correction:
+            w["correction"] = vec(self.E)
         return w
 
     def load(self, t):
         # the shared expert's gate is one more row of the router's matrix: its logit comes with the experts'
-        self.w_router = torch.cat([t["router"], t["shared.sg"].to(t["router"].dtype)], 0).contiguous() if self.shared \
-            else t["router"]
-        dt = matmul_dtype(*(v for k, v in t.items() if k not in ("router", "shared.sg")))
+        self.w_router = torch.cat([t["router"], t["shared.sg"].to(t["router"].dtype)], 0).contiguous() \
+            if self.shared and self.shared_gate else t["router"]
+        self.w_correction = t.get("correction")
+        dt = matmul_dtype(*(v for k, v in t.items() if k not in ("router", "shared.sg", "correction")))
         self.w_up = torch.stack([t[f"e{e}.up"].to(dt) for e in range(self.E)], 0).contiguous()
         self.w_down = torch.stack([t[f"e{e}.down"].to(dt) for e in range(self.E)], 0).contiguous()
         if self.shared:
@@ -305,6 +337,8 @@ class SigmoidTopKMoE(FeedForward):
 
     def router_request(self, n_rows):
         """Routing can ride on the norm before this part (the normalised row is in registers there)."""
+        if self.weighting == "output":
+            return None          # the grouped rule runs as a kernel of its own
         dev, k, extra = self.w_router.device, self.top, 1 if self.shared else 0
         return RouterRequest(self.w_router, 0.0, torch.empty((n_rows, k), dtype=torch.int32, device=dev),
                              torch.empty((n_rows, k), dtype=torch.float32, device=dev), top=k, rule="sigmoid", extra=extra,
@@ -317,6 +351,8 @@ class SigmoidTopKMoE(FeedForward):
         ops = self.ops
         xa = x[self.w_up.dtype]
         T, dev, k, extra = xa.shape[0], xa.device, self.top, 1 if self.shared else 0
+        if self.weighting == "output":
+            return self._forward_output_weighted(x, xa, step)
         if routed is not None:
             # what the pending rows are weighted by when they are added: 1 for the experts (their score went into
             # their input), the sigmoid gate for the shared expert
@@ -344,3 +380,37 @@ class SigmoidTopKMoE(FeedForward):
             step.record.setdefault("gates", []).append(scores)
             step.record.setdefault("router_logits", []).append(logits)
         return Pending(y=y, row_of=row_of, gates=weights)
+
+    def _forward_output_weighted(self, x, xa, step):
+        """The chosen experts' outputs times their weights, and the shared expert's output as one more row a token
+        with weight 1."""
+        ops = self.ops
+        T, dev, k, extra = xa.shape[0], xa.device, self.top, 1 if self.shared else 0
+        ids = torch.empty((T, k), dtype=torch.int32, device=dev)
+        weights = torch.empty((T, k + extra), dtype=torch.float32, device=dev)
+        logits = torch.empty((T, self.E), dtype=torch.float32, device=dev) if step.record is not None else None
+        gates = weights[:, :k] if not extra else torch.empty((T, k), dtype=torch.float32, device=dev)
+        ops.router_sigmoid_grouped(x[torch.float32], self.w_router, self.w_correction, k, self.groups, self.keep,
+                                   self.normalize, self.router_scale, ids, gates, logits)
+        plan, xs = ops.moe_dispatch(ids, self.E, ops.moe_tile_rows(T, self.E, self.w_up.dtype, k), xa)
+        a = torch.empty((k * T, self.inter), dtype=self.w_up.dtype, device=dev)
+        ops.row_act(ops.gemm_partials(xs, self.w_up, plan=plan), a, self.act)
+        y = torch.empty(((k + extra) * T, self.hidden), dtype=torch.float32, device=dev)
+        ops.grouped_gemm(a, self.w_down, y[:k * T], plan, plan_ready=True)
+        row_of = plan.row_of
+        if self.shared:
+            b = torch.empty((T, self.shared), dtype=self.w_up.dtype, device=dev)
+            ops.row_act(ops.gemm_partials(xa, self.w_sup), b, self.act)
+            ops.gemm(b, self.w_sdown, y[k * T:])
+            row_of, weights = self._with_shared_row(row_of, gates, T, k, dev)
+        if step.record is not None:
+            step.record.setdefault("experts", []).append(ids)
+            step.record.setdefault("gates", []).append(gates)
+            step.record.setdefault("router_logits", []).append(logits)
+        return Pending(y=y, row_of=row_of, gates=weights)
+
+    def _with_shared_row(self, row_of, gates, T, k, dev):
+        """(row_of, weights) with one more column: the shared expert's row of every token, weight 1."""
+        own = torch.arange(k * T, (k + 1) * T, dtype=torch.int32, device=dev)
+        return (torch.cat([row_of, own[:, None]], 1).contiguous(),
+                torch.cat([gates, torch.ones((T, 1), dtype=torch.float32, device=dev)], 1).contiguous())

@@ -1,6 +1,9 @@
 """Two mixers that carry a matrix of state per head from token to token: the gated delta rule and a state-space
 model with a scalar decay per head (the state-space duality form of Mamba-2).
 
+A third, ``retention``, is linear attention with a fixed decay per head: S <- decay_h S + k v^T, o = S^T q, with q and
+k rotated by the position; it runs the state-space form of the same kernel with the decay and the step size constant.
+
 Both keep, per request, a float32 matrix S per head and the last ``taps - 1`` inputs of a short causal convolution
 in one row of the cache manager's state slab (zeroed on admission), and both run the same recurrence kernel
 (``ops.recurrence_scan``), which walks every request's rows of the step in order from the state its earlier steps
@@ -136,6 +139,76 @@ class GatedDeltaRule(_Recurrent):
         act = self.ctx.act_dtype if self.w_o.dtype == torch.bfloat16 else torch.float32
         out = torch.empty((T, H * V), dtype=act, device=dev)
         ops.gated_norm(o, gate, "sigmoid", False, self.w_norm, self.eps, H, out)
+        return Pending(partials=ops.gemm_partials(out, self.w_o))
+
+
+@MIXERS.register("retention")
+class Retention(_Recurrent):
+    """Linear attention with a fixed decay per head and no softmax or denominator: per head S <- decay_h S + k v^T,
+    o = S^T q, where q and k rotate by the position over their leading dims and k is scaled by dim^(-1/2); each head's o
+    is divided by its root mean square (no scale), the heads side by side are multiplied by silu(W_g x) and projected.
+    The state (S per head, float32) is a ``StateSpec`` slab zeroed at admission.
+
+    params: hidden_size, num_heads, dim, value_dim, decay (one number a head), norm_eps, position (PartSpec or None).
+    tensors: q, k [H dim, hidden]; v, g [H value_dim, hidden]; o [hidden, H value_dim]."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        from .attention import shared_position_encoding
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.H, self.D, self.V = int(p["num_heads"]), int(p["dim"]), int(p["value_dim"])
+        if self.D > 256:
+            raise ConfigError(f"retention: {self.D} key dims per head are not supported (up to 256)")
+        decay = [float(x) for x in p["decay"]]
+        if len(decay) != self.H:
+            raise ConfigError(f"retention: {len(decay)} decays for {self.H} heads")
+        self.decay = torch.tensor(decay, dtype=torch.float32, device=ctx.device)
+        self.eps = float(p["norm_eps"])
+        self.position = shared_position_encoding(p["position"], ctx) if p.get("position") is not None else None
+        self.rot = self.position.rotary_dim if self.position is not None else 0
+        if self.rot > self.D:
+            raise ConfigError("retention: rotary_dim exceeds dim")
+        self.ones = torch.ones(self.V, dtype=torch.float32, device=ctx.device)
+
+    def weights(self):
+        H, D, V, W = self.H, self.D, self.V, self.hidden
+        return {"q": mat(H * D, W), "k": mat(H * D, W), "v": mat(H * V, W), "g": mat(H * V, W), "o": mat(W, H * V)}
+
+    def load(self, t):
+        names = ("q", "k", "v", "g")
+        dt = matmul_dtype(*(t[n] for n in names), t["o"])
+        self.w_in = torch.cat([t[n].to(dt) for n in names], 0).contiguous()      # one product gives q, k, v and the gate
+        self.w_o = t["o"].to(dt)
+        self.cos, self.sin = self.position.tables() if self.position is not None else (None, None)
+
+    def input_dtypes(self):
+        return (self.w_in.dtype,)
+
+    def state_spec(self):
+        return StateSpec((self.H * self.D * self.V,), torch.float32)
+
+    def forward(self, x, residual, step, cache, state, writes_cache=True):
+        ops, H, D, V = self.ops, self.H, self.D, self.V
+        if state is None:
+            raise ModelError("retention needs a state slab")
+        xin = x[self.w_in.dtype]
+        T, dev = xin.shape[0], xin.device
+        f32 = dict(dtype=torch.float32, device=dev)
+        proj = torch.empty((T, self.w_in.shape[0]), **f32)
+        ops.gemm(xin, self.w_in, proj)
+        qk = torch.empty((T, 2 * H * D), **f32)
+        decay, dt = torch.empty((T, H), **f32), torch.empty((T, H), **f32)
+        # the key's scale rides on the step size: S <- decay S + k (dt v)^T
+        ops.retention_prepare(proj, step.pos, self.cos, self.sin, self.rot,
+                              self.position.style if self.position is not None else "half", self.decay, D ** -0.5, qk, decay,
+                              dt, H, D)
+        o = torch.empty((T, H * V), **f32)
+        ops.recurrence_scan(qk[:, :H * D], qk[:, H * D:], proj[:, 2 * H * D:2 * H * D + H * V], decay, False, None, dt, None,
+                            step.slot, request_starts(step), len(step.entries), state, o, H, H, D, V)
+        act = self.ctx.act_dtype if self.w_o.dtype == torch.bfloat16 else torch.float32
+        out = torch.empty((T, H * V), dtype=act, device=dev)
+        ops.gated_norm(o, proj[:, 2 * H * D + H * V:], "silu", False, self.ones, self.eps, H, out)
         return Pending(partials=ops.gemm_partials(out, self.w_o))
 
 

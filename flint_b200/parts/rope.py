@@ -1,4 +1,4 @@
-"""Rotary position encoding with optional LongRoPE scaling.
+"""Rotary position encoding with optional LongRoPE or YaRN scaling.
 
 The cos/sin tables are built on the host in float64 and stored as float32
 [positions, rotary_dim/2]: inv_i = theta^(-2i/rot), divided by the short factor for
@@ -12,6 +12,8 @@ style "interleaved", dims 2i and 2i + 1) is done by the kernel that also writes 
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..errors import ConfigError
@@ -22,8 +24,12 @@ from .base import PositionEncoding
 @POSITION_ENCODINGS.register("rope")
 class RotaryEncoding(PositionEncoding):
     """params: rotary_dim, theta, max_positions, style ("half", the default, or "interleaved"), and for LongRoPE:
-    short_factor, long_factor, original_max_positions, short_mscale, long_mscale.  The tables cover the positions
-    the model is built to serve (``BuildContext.max_context``) when that is fewer than ``max_positions``."""
+    short_factor, long_factor, original_max_positions, short_mscale, long_mscale.  For YaRN: ``yarn`` = {factor,
+    original, fast, slow}: with dim(t) = rot ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(dim(fast)), 0),
+    hi = min(ceil(dim(slow)), rot - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), frequency i is
+    inv_i / factor * ramp_i + inv_i (1 - ramp_i), and cos and sin are multiplied by 0.1 ln(factor) + 1.  The tables
+    cover the positions the model is built to serve (``BuildContext.max_context``) when that is fewer than
+    ``max_positions``."""
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -55,6 +61,17 @@ class RotaryEncoding(PositionEncoding):
                 ang = pos[:, None] * torch.where(is_short, inv / short, inv / long)
                 scale = torch.where(is_short, torch.tensor(float(p.get("short_mscale", 1.0)), dtype=torch.float64),
                                     torch.tensor(float(p.get("long_mscale", 1.0)), dtype=torch.float64))
+            elif p.get("yarn") is not None:
+                y = p["yarn"]
+                factor, original = float(y["factor"]), float(y["original"])
+                if factor <= 0 or original <= 0 or float(y["fast"]) <= 0 or float(y["slow"]) <= 0 or self.theta <= 1:
+                    raise ConfigError("YaRN: factor, original, fast and slow must be positive (and theta above 1)")
+                where = lambda t: self.rotary_dim * math.log(original / (2 * math.pi * t)) / (2 * math.log(self.theta))
+                lo = max(math.floor(where(float(y["fast"]))), 0)
+                hi = min(math.ceil(where(float(y["slow"]))), self.rotary_dim - 1)
+                ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0, 1)
+                ang = pos[:, None] * (inv / factor * ramp + inv * (1 - ramp))[None, :]
+                scale = torch.full((1, 1), 0.1 * math.log(factor) + 1, dtype=torch.float64)
             else:
                 ang = pos[:, None] * inv[None, :]
                 scale = torch.ones((1, 1), dtype=torch.float64)

@@ -249,7 +249,7 @@ class RefOps:
         cache.v[pages, :, p % P, :] = v.to(cache.v.dtype)
 
     def sink_attention(self, q, cache, step, out, nq, nkv, hd, vd, window, keep_first, sinks, scale, splits=None,
-                       tiling=None, rows=None, chunk=0):
+                       tiling=None, rows=None, chunk=0, pool=0, sigmoid=None):
         T, P, G = q.shape[0], cache.page_size, nq // nkv
         qq = q.to(self.cd).view(T, nq, hd)
         res = torch.zeros(T, nq, vd, dtype=self.cd)
@@ -263,11 +263,28 @@ class RefOps:
             assert (pages >= 0).all(), f"row {t}: key without a page"
             k = cache.k[pages, :, js % P, :].to(self.cd)
             v = cache.v[pages, :, js % P, :].to(self.cd)
+            if pool and p - window + 1 >= pool:        # the means of the blocks that lie wholly before the window
+                bs = torch.arange((p - window + 1) // pool)
+                E = cache.pool_slots
+                homes = cache.block_table[int(step.slot[t]), bs // E].long()
+                assert (homes >= 0).all(), f"row {t}: block mean without a page"
+                k = torch.cat([cache.pool_k[homes, :, bs % E, :].to(self.cd), k], 0)
+                v = torch.cat([cache.pool_v[homes, :, bs % E, :].to(self.cd), v], 0)
             for h in range(nq):
                 s = (k[:, h // G, :] @ qq[t, h]) * scale
+                if sigmoid is not None:
+                    cap, r1, r2, bias = sigmoid
+                    if cap:
+                        s = cap * torch.tanh(s / cap)
+                    if r1 is not None:
+                        s = s - r1[h].to(self.cd) * torch.log(1 + r2[h].to(self.cd) * (p - js).to(self.cd))
+                    if bias is not None:
+                        s = s + bias[h].to(self.cd)
+                    res[t, h] = torch.sigmoid(s) @ v[:, h // G, :]
+                    continue
                 if sinks is not None:
                     s = torch.cat([s, sinks[h].to(self.cd).view(1)])
-                w = torch.softmax(s, 0)[:js.numel()]
+                w = torch.softmax(s, 0)[:k.shape[0]]
                 res[t, h] = w @ v[:, h // G, :]
         out.copy_(res.reshape(T, nq * vd).to(out.dtype))
 
@@ -457,16 +474,22 @@ class RefOps:
         return torch.cat([both, h[..., rot:]], -1)
 
     def qk_norm_write(self, y, q_norm, k_norm, eps, pos, slot, cos, sin, rot, style, v_cos, v_sin, v_style, q_out, cache,
-                      nq, nkv, hd, vd, status):
+                      nq, nkv, hd, vd, status, whole=False, v_from_k=False, q_temp=None):
         T = y.shape[0]
         x = y.to(self.cd)
         p = pos.long()
-        q = x[:, :nq * hd].view(T, nq, hd)
-        k = x[:, nq * hd:(nq + nkv) * hd].view(T, nkv, hd)
-        v = x[:, (nq + nkv) * hd:(nq + nkv) * hd + nkv * vd].view(T, nkv, vd)
-        if q_norm is not None:
+        q = x[:, :nq * hd].reshape(T, nq, hd)
+        k = x[:, nq * hd:(nq + nkv) * hd].reshape(T, nkv, hd)
+        v = k.clone() if v_from_k else x[:, (nq + nkv) * hd:(nq + nkv) * hd + nkv * vd].reshape(T, nkv, vd)
+        if q_norm is not None and whole:
+            q = (q / torch.sqrt((q * q).mean((-2, -1), keepdim=True) + eps)) * q_norm.to(self.cd).view(nq, hd)
+            k = (k / torch.sqrt((k * k).mean((-2, -1), keepdim=True) + eps)) * k_norm.to(self.cd).view(nkv, hd)
+        elif q_norm is not None:
             q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps) * q_norm.to(self.cd)
             k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps) * k_norm.to(self.cd)
+        if q_temp is not None:
+            temp = 1 + q_temp[0] * torch.log(torch.floor((p.to(self.cd) + 1) / q_temp[1]) + 1)
+            q = q * temp[:, None, None]
         if rot:
             q = self._turn(q, cos[p].to(self.cd), sin[p].to(self.cd), style)
             k = self._turn(k, cos[p].to(self.cd), sin[p].to(self.cd), style)
@@ -485,9 +508,72 @@ class RefOps:
         if v_cos is not None:
             p = pos.long()
             x = self._turn(x, v_cos[p].to(self.cd), v_sin[p].to(self.cd), v_style, sign=-1.0)
-        if gate is not None:
+        if gate is not None and gate.shape[1] == nq * vd and vd > 1:
+            x = x * torch.sigmoid(gate.to(self.cd)).view(T, nq, vd)
+        elif gate is not None:
             x = x * torch.sigmoid(gate.to(self.cd))[:, :, None]
         out.copy_(x.reshape(T, nq * vd).to(out.dtype))
+
+    # ------------------------------------------------------------------ means of blocks, weighted sums, retention, grouped sigmoid router
+    def pool_write(self, cache, step, nkv, hd, vd, pool):
+        P, E = cache.page_size, cache.pool_slots
+        for t in range(step.n_tokens):
+            p, sl = int(step.pos[t]), int(step.slot[t])
+            if (p + 1) % pool:
+                continue
+            b = (p + 1) // pool - 1
+            js = torch.arange(b * pool, p + 1)
+            pages = cache.block_table[sl, js // P].long()
+            assert (pages >= 0).all(), "a block's position without a page"
+            home = int(cache.block_table[sl, b // E])
+            assert home >= 0
+            cache.pool_k[home, :, b % E, :] = cache.k[pages, :, js % P, :].to(self.cd).mean(0).to(cache.pool_k.dtype)
+            cache.pool_v[home, :, b % E, :] = cache.v[pages, :, js % P, :].to(self.cd).mean(0).to(cache.pool_v.dtype)
+
+    def sum_norm_add(self, dst, branches=(), scales=(), expert_rows=None, gamma=None, eps=0.0, accumulate=True):
+        r = torch.zeros(dst.shape, dtype=self.cd)
+        for (part, bias), sc in zip(branches, scales):
+            y = part.to(self.cd).sum(0)
+            if bias is not None:
+                y = y + bias.to(self.cd)
+            r = r + sc * y
+        if expert_rows is not None:
+            y, row_of, gates = expert_rows
+            r = r + (y.to(self.cd)[row_of.long()] * gates.to(self.cd)[:, :, None]).sum(1)
+        if gamma is not None:
+            r = r / torch.sqrt((r * r).mean(-1, keepdim=True) + eps) * gamma.to(self.cd)
+        dst.copy_(((dst.to(self.cd) if accumulate else 0) + r).to(dst.dtype))
+
+    def retention_prepare(self, proj, pos, cos, sin, rot, style, decay_h, dt_value, qk, decay, dt, H, D):
+        T = proj.shape[0]
+        x = proj[:, :2 * H * D].to(self.cd).reshape(T, 2 * H, D)
+        if rot:
+            p = pos.long()
+            x = self._turn(x, cos[p].to(self.cd), sin[p].to(self.cd), style)
+        qk.copy_(x.reshape(T, 2 * H * D).to(qk.dtype))
+        decay.copy_(decay_h.to(decay.dtype)[None, :].expand(T, H))
+        dt.fill_(dt_value)
+
+    def router_sigmoid_grouped(self, x, wr, correction, top, n_groups, keep, normalize, scale, expert_ids, gates,
+                               logits_out=None):
+        z = x.to(self.cd) @ wr.to(self.cd).T
+        T, E = z.shape
+        s = torch.sigmoid(z)
+        c = s + correction.to(self.cd) if correction is not None else s.clone()
+        per = E // n_groups
+        if keep < n_groups:
+            gs = c.view(T, n_groups, per).topk(min(2, per), -1).values.sum(-1)
+            order = torch.sort(gs, dim=-1, descending=True, stable=True).indices[:, :keep]
+            kept = torch.zeros((T, n_groups), dtype=torch.bool).scatter_(1, order, True)
+            c = c.masked_fill(~kept[:, :, None].expand(T, n_groups, per).reshape(T, E), -math.inf)
+        idx = torch.sort(c, dim=-1, descending=True, stable=True).indices[:, :top]
+        val = s.gather(1, idx)
+        if normalize:
+            val = val / (val.sum(-1, keepdim=True) + 1e-20)
+        expert_ids.copy_(idx.to(torch.int32))
+        gates.copy_((val * scale).to(gates.dtype))
+        if logits_out is not None:
+            logits_out.copy_(z.to(logits_out.dtype))
 
     # ------------------------------------------------------------------ sigmoid router, plain experts
     def router_sigmoid(self, x, wr, E, top, expert_ids, scores, weights, logits_out=None):
