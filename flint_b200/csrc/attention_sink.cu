@@ -413,7 +413,9 @@ __global__ void __launch_bounds__(128)
 sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                           const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table, int max_pages,
                           int page_size, const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int nq, int nkv, int hd,
-                          int vd, int window, int keep_first, int run, const float* __restrict__ sinks, float scale) {
+                          int vd, int window, int keep_first, int run, const float* __restrict__ sinks, float scale,
+                          const __nv_bfloat16* __restrict__ pool_k, const __nv_bfloat16* __restrict__ pool_v, int pool,
+                          int pool_slots, SigmoidWeights sw) {
   extern __shared__ __align__(16) unsigned char sm_raw[];
   const int ldk = hd + 8, ldv = vd + 8;
   // two stages, each keys [MK][ldk], values [MK][ldv] and the keys' positions [MK] (or -1); the first stage's keys
@@ -449,7 +451,10 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
   const int p_last = p0 + n_rows - 1;
   const int lo_first = run > 0 ? (p0 / run) * run : (window > 0 ? max(0, p0 + 1 - window) : 0);
   const bool gap = (window > 0 || run > 0) && lo_first > keep_first;  // kept keys and window do not touch
-  const int n_first = gap ? keep_first : 0, base = gap ? lo_first : 0;
+  // with block means: first the means the tile's last row sees (a key "position" -2 - b stands for block b), then
+  // the positions from the first row's window start on
+  const int n_first = pool > 0 ? max(0, (p_last - window + 1) / pool) : (gap ? keep_first : 0);
+  const int base = pool > 0 ? lo_first : (gap ? lo_first : 0);
   const int total = n_first + (p_last + 1 - base);
   const int* bt = block_table + (size_t)slot * max_pages;
   const int r_lo = warp * 16 + g;                                      // this thread's two rows: r_lo and r_lo + 8
@@ -469,18 +474,20 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
     int* pos_d = reinterpret_cast<int*>(v_d + MK * ldv);
     auto key_at = [&](int r) {
       const int u = u0 + r;
-      return u < total ? (u < n_first ? u : base + (u - n_first)) : -1;
+      return u < total ? (u < n_first ? (pool > 0 ? -2 - u : u) : base + (u - n_first)) : -1;
     };
     // two threads a key: the key's position and page are worked out once, then the row's 16-byte pieces alternate
     const int r = tid >> 1, half = tid & 1, j = key_at(r);
     if (half == 0) pos_d[r] = j;
-    const int page = j >= 0 ? bt[j / page_size] : -1;
+    const int blk = -2 - j;                    // the block whose means stand at this place, if j <= -2
+    const int page = j >= 0 ? bt[j / page_size] : (j <= -2 ? bt[blk / pool_slots] : -1);
     __nv_bfloat16* kd = k_d + r * ldk;
     __nv_bfloat16* vd_ = v_d + r * ldv;
     if (page >= 0) {
-      const size_t at = ((size_t)page * nkv + kvh) * page_size + j % page_size;
-      const __nv_bfloat16* ks = k_cache + at * hd;
-      const __nv_bfloat16* vs = v_cache + at * vd;
+      const size_t at = j >= 0 ? ((size_t)page * nkv + kvh) * page_size + j % page_size
+                               : ((size_t)page * nkv + kvh) * pool_slots + blk % pool_slots;
+      const __nv_bfloat16* ks = (j >= 0 ? k_cache : pool_k) + at * hd;
+      const __nv_bfloat16* vs = (j >= 0 ? v_cache : pool_v) + at * vd;
       for (int c = half; c < chunks_k; c += 2) copy16(kd + c * 8, ks + c * 8);
       for (int c = half; c < chunks_v; c += 2) copy16(vd_ + c * 8, vs + c * 8);
     } else {
@@ -523,9 +530,25 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
     // mask, scale, and this tile's maxima of the thread's two rows.  Most tiles lie behind every row of the tile and
     // inside every row's window: they need no mask
     float mx[2] = {-INFINITY, -INFINITY};
-    const bool interior = kpos[MK - 1] >= 0 && kpos[MK - 1] <= p0 && (window == 0 || p_last - kpos[0] < window) &&
-                          (run == 0 || kpos[0] >= (p_last / run) * run);
-    if (interior) {
+    const bool interior = !sw.on &&
+        ((kpos[0] >= 0 && kpos[MK - 1] >= 0 && kpos[MK - 1] <= p0 && (window == 0 || p_last - kpos[0] < window) &&
+          (run == 0 || kpos[0] >= (p_last / run) * run)) ||
+         (kpos[MK - 1] <= -2 && (-1 - kpos[MK - 1]) * pool <= p0 - window + 1));     // or means that every row sees
+    if (sw.on) {
+      // no softmax: a key's weight is sigmoid(cap tanh(score / cap) - r1 ln(1 + r2 distance) + bias), not normalised
+      const float r1 = sw.r1 ? sw.r1[h] : 0.f, r2 = sw.r2 ? sw.r2[h] : 0.f, wb = sw.bias ? sw.bias[h] : 0.f;
+#pragma unroll
+      for (int nt = 0; nt < MK / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = kpos[nt * 8 + 2 * tq + (e & 1)], rs = e >> 1, p = p_row[rs];
+          const bool ok = j >= 0 && row_ok[rs] && j <= p && (window == 0 || p - j < window);
+          float z = s[nt][e] * scale;
+          if (sw.cap > 0.f) z = sw.cap * (1.0f - 2.0f / (__expf(2.0f * z / sw.cap) + 1.0f));
+          if (sw.r1) z -= r1 * __logf(1.0f + r2 * (float)(p - j));
+          s[nt][e] = ok ? 1.0f / (1.0f + __expf(-(z + wb))) : 0.f;
+        }
+    } else if (interior) {
 #pragma unroll
       for (int nt = 0; nt < MK / 8; ++nt)
 #pragma unroll
@@ -539,13 +562,15 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int j = kpos[nt * 8 + 2 * tq + (e & 1)], rs = e >> 1, p = p_row[rs];
-          const bool ok = j >= 0 && row_ok[rs] && j <= p && (window == 0 || p - j < window || j < keep_first) &&
-                          (run == 0 || j >= (p / run) * run);
+          const bool ok = j <= -2 ? row_ok[rs] && (-1 - j) * pool <= p - window + 1
+                                  : j >= 0 && row_ok[rs] && j <= p && (window == 0 || p - j < window || j < keep_first) &&
+                                        (run == 0 || j >= (p / run) * run);
           s[nt][e] = ok ? s[nt][e] * scale : -INFINITY;
           mx[rs] = fmaxf(mx[rs], s[nt][e]);
         }
     }
-    float alpha[2];
+    float alpha[2] = {1.f, 1.f};
+    if (!sw.on) {
 #pragma unroll
     for (int rs = 0; rs < 2; ++rs) {
       mx[rs] = fmaxf(mx[rs], __shfl_xor_sync(0xffffffffu, mx[rs], 1));
@@ -575,6 +600,7 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
       o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0];
       o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
     }
+    }
 #pragma unroll
     for (int kk = 0; kk < MK / 16; ++kk) {
       const uint32_t a[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
@@ -596,7 +622,8 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
   for (int rs = 0; rs < 2; ++rs) {
     if (!row_ok[rs]) continue;
     float so = 1.f, sum = l_r[rs];
-    if (sinks) {
+    if (sw.on) sum = 1.f;
+    else if (sinks) {
       const float sk = sinks[h], m_all = fmaxf(m_r[rs], sk);
       so = m_r[rs] > -INFINITY ? expf(m_r[rs] - m_all) : 0.f;
       sum = l_r[rs] * so + expf(sk - m_all);
@@ -703,13 +730,21 @@ extern "C" int flint_sink_attention(const void* q, int q_dtype, const void* k_ca
 extern "C" int flint_sink_attention_tiles(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                                           int max_pages, int page_size, const int* tiles, int n_tiles, void* out, int nq,
                                           int nkv, int hd, int vd, int window, int keep_first, int run,
-                                          const float* sinks, float scale, cudaStream_t stream) {
+                                          const float* sinks, float scale, const void* pool_k, const void* pool_v,
+                                          int pool, int pool_slots, int sigmoid, float cap, const float* r1,
+                                          const float* r2, const float* w_bias, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (hd < 16 || vd < 16 || hd % 16 || vd % 16 || hd > 128 || vd > 128)
     return fail("sink_attention_tiles: head sizes %d and %d (multiples of 16 up to 128)", hd, vd);
   if (nkv <= 0 || nq % nkv) return fail("sink_attention_tiles: %d query heads do not divide into %d kv heads", nq, nkv);
   if (window < 0 || keep_first < 0 || page_size <= 0 || run < 0 || (run > 0 && (window > 0 || keep_first > 0)))
     return fail("sink_attention_tiles: bad window or page size");
+  if (pool < 0 || (pool > 0 && (window < 1 || keep_first > 0 || run > 0 || !pool_k || !pool_v || pool_slots < 1)))
+    return fail("sink_attention_tiles: block means need a window, their storage, and no kept first tokens or runs");
+  if (sigmoid && (sinks || (r1 == nullptr) != (r2 == nullptr)))
+    return fail("sink_attention_tiles: weights without a softmax take no sink, and both numbers of the penalty or none");
+  const SigmoidWeights sw = {sigmoid ? 1 : 0, cap, r1, r2, w_bias};
+  const __nv_bfloat16 *pk = (const __nv_bfloat16*)pool_k, *pv = (const __nv_bfloat16*)pool_v;
   if ((long long)n_tiles * nq > 0x7fffffffLL) return fail("sink_attention_tiles: too many work items");
   const size_t smem = 2 * ((size_t)MK * ((hd + 8) + (vd + 8)) * 2 + MK * sizeof(int));       // two stages
   const dim3 grid((unsigned)(n_tiles * nq)), block(128);
@@ -722,10 +757,10 @@ extern "C" int flint_sink_attention_tiles(const void* q, const void* k_cache, co
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_cache, *vv = (const __nv_bfloat16*)v_cache;
   if (hd <= 64 && vd <= 64)
     launch_pdl(sink_attention_mma_kernel<4, 8>, grid, block, smem, stream, qq, kk, vv, block_table, max_pages, page_size, tiles,
-               (__nv_bfloat16*)out, nq, nkv, hd, vd, window, keep_first, run, sinks, scale);
+               (__nv_bfloat16*)out, nq, nkv, hd, vd, window, keep_first, run, sinks, scale, pk, pv, pool, pool_slots, sw);
   else
     launch_pdl(sink_attention_mma_kernel<8, 16>, grid, block, smem, stream, qq, kk, vv, block_table, max_pages, page_size, tiles,
-               (__nv_bfloat16*)out, nq, nkv, hd, vd, window, keep_first, run, sinks, scale);
+               (__nv_bfloat16*)out, nq, nkv, hd, vd, window, keep_first, run, sinks, scale, pk, pv, pool, pool_slots, sw);
   return check_launch("sink_attention_tiles");
 }
 

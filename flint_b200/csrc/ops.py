@@ -826,13 +826,15 @@ class CudaOps:
             _check(sinks, "sinks", torch.float32, 1)
             if sinks.numel() != nq:
                 raise KernelError(f"sink_attention: sinks must have {nq} entries")
-        if (tiling is not None and tiling.n_tiles > 0 and rows is None and splits is None and not pool and sigmoid is None
+        if (tiling is not None and tiling.n_tiles > 0 and rows is None and splits is None
                 and self.sink_attention_tiles_ok(q.dtype, cache.k.dtype, hd, vd)):
             _check(tiling.tiles, "tiles", torch.int32)
             self._run("attention_sink", "flint_sink_attention_tiles", _ptr(q), _ptr(cache.k), _ptr(cache.v),
                       _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(P), _ptr(tiling.tiles),
                       c_int(tiling.n_tiles), _ptr(out), c_int(nq), c_int(nkv), c_int(hd), c_int(vd), c_int(window),
-                      c_int(keep_first), c_int(chunk), _ptr(sinks), c_float(scale))
+                      c_int(keep_first), c_int(chunk), _ptr(sinks), c_float(scale), _ptr(cache.pool_k if pool else None),
+                      _ptr(cache.pool_v if pool else None), c_int(pool), c_int(cache.pool_slots if pool else 0),
+                      c_int(1 if sigmoid is not None else 0), c_float(cap), _ptr(r1), _ptr(r2), _ptr(w_bias))
             if not tiling.n_other_rows:
                 return
             rows = tiling.other_rows

@@ -365,6 +365,8 @@ class Model:
             owner = i if call.cache_of is None else call.cache_of
             carry = layer.block.forward(h, step, self.cache.view(owner), self.cache.state_of(i),
                                         writes_cache=call.cache_of is None, carry=carry)
+            if step.record is not None and carry is None and history is None:
+                step.record.setdefault("rows_after", []).append(h.clone())      # the rows as this call leaves them
             if history is not None:
                 if carry is not None:
                     ops.apply_pending(h, carry)

@@ -229,8 +229,7 @@ class Attention(Mixer):
         if not self.general:
             return self.NEEDS
         ok = getattr(self.ops, "sink_attention_tiles_ok", None)
-        tiles = (ok is not None and ok(self.ctx.act_dtype, self.ctx.act_dtype, self.hd, self.vd)
-                 and not self.pool and self.weights_rule != "sigmoid")
+        tiles = ok is not None and ok(self.ctx.act_dtype, self.ctx.act_dtype, self.hd, self.vd)
         return self.NEEDS_GENERAL if tiles else None
 
     def plan_step(self, step, captured):
