@@ -603,6 +603,134 @@ def run_tefovik_pair(args, pk, rng):
     return out
 
 
+def dumizen_config(width, heads, kv_heads, dim, vdim, window, pool, rot, r_heads, r_dim, r_vdim, ff, experts, top, groups, keep,
+                   shared, layers, vocab):
+    """A Dumizen configuration of ``layers`` layers in the order sigmoid attention, pooled-window attention, parallel
+    mixer (gated sink attention beside a retention), pooled-window attention, ...; layers 2 .. 5 run twice (a model
+    of 8 layers makes 12 layer runs); every layer with a mixture of squared-ReLU experts and a shared one."""
+    yarn = {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+    out = []
+    for i in range(layers):
+        head = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "scale": dim ** -0.5}
+        if i % 4 == 0:
+            kind, m = "attention_2", {**head, "vdim": vdim, "softcap": 30.0, "q_temp": {"coef": 0.1, "every": 1024}}
+        elif i % 4 == 2:
+            kind = "parallel"
+            m = {"left": {**head, "vdim": dim, "rot": {"dims": dim, "base": 5e5, "scaling": yarn}},
+                 "right": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "rot": {"dims": r_dim, "base": 1e6},
+                           "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(r_heads - 1, 1)) for h in range(r_heads)]},
+                 "left_scale": 1.0, "right_scale": 1.0}
+        else:
+            kind, m = "attention", {**head, "vdim": vdim, "mask": {"size": window, "pool": pool},
+                                    "rot": {"dims": rot, "base": 1e4, "scaling": yarn}}
+        mlp = {"kind": "moe", "expert": {"ff": ff}, "shared": {"ff": shared},
+               "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": groups, "keep": keep}}}
+        out.append({"type": kind, "mixer": m, "mlp": mlp})
+    cfg = {"architecture": "Dumizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
+    if layers >= 6:
+        cfg["loop"] = {"start": 2, "stop": 6, "times": 2}
+    return cfg
+
+
+# layer sizes that resemble real models of this kind, beside a Gepadra of equal width and as many layers as the Dumizen
+# has layer runs, whose attention layers (every second one) have the same heads and window, whose mLSTM heads hold a
+# state of the retention's shape, and whose experts have the same sizes
+DUMIZEN_SIZES = {
+    "2048x16": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, pool=64, rot=64, r_heads=16, r_dim=128,
+                    r_vdim=128, ff=1408, experts=16, top=2, groups=4, keep=2, shared=2816,
+                    gepadra=dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep=8, rot=64, m_heads=16,
+                                 m_dim=128, m_vdim=128, ff=1408, experts=16, top=2, shared=2816, dense_ff=5632, every=2)),
+    "4096x32": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, pool=64, rot=64, r_heads=32, r_dim=128,
+                    r_vdim=128, ff=1408, experts=32, top=4, groups=4, keep=2, shared=2816,
+                    gepadra=dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, keep=8, rot=64, m_heads=32,
+                                 m_dim=128, m_vdim=128, ff=1408, experts=32, top=4, shared=2816, dense_ff=11264, every=2)),
+}
+
+
+def run_dumizen_pair(args, pk, rng):
+    """Prefill and decode of Dumizen at layer sizes that resemble real models, beside Gepadra at equal width, heads,
+    window and state shape and as many layers as the Dumizen has layer runs: tokens/s, and for the attention and
+    recurrence kernels of both the time a layer run and the distance from the roofline (decode: cache or state bytes
+    over the measured copy bandwidth; prefill attention: flops over the sustained library product rate; prefill
+    recurrences, which walk tokens in float32 on the plain pipes: flops over the chip's float32 multiply-add rate)."""
+    import torch
+    layers = args.layers or 8
+    vocab = args.vocab or 32064
+    batch, ctx = args.batch, args.prompt_tokens
+    fp32_rate = FP32_FMA_LANES * 2 * 1.965e9
+    out = {"design": "Dumizen", "beside": "Gepadra", "layers": layers, "batch": batch, "prompt_tokens": ctx, "dtype": "bf16",
+           "data": "synthetic: seeded random weights, uniform-random token ids",
+           "peaks": {**{k: pk[k] for k in ("hbm_gbs", "bf16_tflops_sustained", "source")},
+                     "fp32_tflops_nominal": round(fp32_rate / 1e12, 1)}, "sizes": {}}
+    for name, sz in DUMIZEN_SIZES.items():
+        if args.design_sizes and name not in args.design_sizes:
+            continue
+        dz = dumizen_config(**{k: v for k, v in sz.items() if k != "gepadra"}, layers=layers, vocab=vocab)
+        runs = layers + (4 if "loop" in dz else 0)
+        cfgs = {"dumizen": dz, "gepadra": gepadra_config(**sz["gepadra"], layers=runs, vocab=vocab)}
+        row = {}
+        for which, cfg in cfgs.items():
+            cfg.setdefault("vocab_size", cfg.get("vocab"))
+            model = build_model(cfg, max(batch, 1), ctx + 256)
+            pre_ms = run_prefill(model, cfg, ctx, reps=3, warmup=3, rng=rng)
+            dec = run_decode(model, cfg, batch, ctx, args.steps, max(args.warmup, 3), rng, count_experts=False)
+            pre_t, dec_t, _ = profile_tables(model, cfg, batch, ctx, rng)
+            kv = ctx + 2
+            called = [model.layers[c.layer].parts["mixer"] for c in model.order]       # the mixer of every layer run
+            kinds = {}          # label of the attention kernel's launches -> (mixer, layer runs, keys a row at k positions sees)
+            if which == "dumizen":
+                for m in called:
+                    a = dict(m.branches)["left"] if hasattr(m, "branches") else m
+                    label = "sigmoid" if a.weights_rule == "sigmoid" else ("pooled" if a.pool else "softmax")
+                    seen = (lambda k, a=a: min(k, a.window) + max(0, (k - a.window) // a.pool)) if a.pool else (lambda k: k)
+                    kinds[label] = (a, kinds.get(label, (None, 0))[1] + 1, seen)
+                ret = next(dict(m.branches)["right"] for m in called if hasattr(m, "branches"))
+                n_rec = sum(1 for m in called if hasattr(m, "branches"))
+                scans = {"ssd": (ret.H * ret.D * ret.V, 5, n_rec)}
+                names = ("flint_sink_attention", "flint_qk_norm_write", "flint_pool_write", "flint_head_finish",
+                         "flint_recurrence_scan", "flint_retention_prepare", "flint_gated_norm", "flint_sum_norm_add",
+                         "flint_router_sigmoid_grouped", "flint_row_act", "flint_row_norm")
+            else:
+                att = next(m for m in called if hasattr(m, "keep_first"))
+                rec = next(m for m in called if hasattr(m, "cap"))
+                n_att = sum(1 for m in called if hasattr(m, "keep_first"))
+                kinds["softmax"] = (att, n_att, lambda k: min(k, att.window + att.keep_first))
+                scans = {"mlstm": (rec.H * (rec.D * rec.V + rec.D + 1), 5, len(called) - n_att)}
+                names = ("flint_sink_attention", "flint_qkv_write", "flint_mlstm", "flint_row_norm", "flint_row_act")
+            kern = {}
+            for kind, table in (("prefill", pre_t), ("decode", dec_t)):
+                for kname, (n, ms) in sorted(table.items()):
+                    if not kname.startswith(names):
+                        continue
+                    scan = next((s for s in scans if kname.startswith(("flint_recurrence_scan " + s, "flint_mlstm_scan"))), None)
+                    label = next((l for l in kinds if kname.startswith("flint_sink_attention") and kname.endswith(" " + l)), None)
+                    per = scans[scan][2] if scan is not None else (kinds[label][1] if label is not None else len(called))
+                    secs = ms / per * 1e-3
+                    e = {"launches": n, "us_per_layer_run": round(ms * 1000.0 / per, 2)}
+                    if scan is not None:
+                        elems, flops, _ = scans[scan]
+                        if kind == "decode":        # the state is read and written once a token
+                            e["frac_of_copy_bandwidth"] = round(batch * elems * 4 * 2 / secs / 1e9 / pk["hbm_gbs"], 4)
+                        else:
+                            e["frac_of_fp32_rate"] = round(ctx * elems * flops / secs / fp32_rate, 4)
+                            e["ns_per_token"] = round(secs * 1e9 / ctx, 1)
+                    elif label is not None and not kname.startswith("flint_sink_combine"):
+                        a, _, seen = kinds[label]
+                        if kind == "decode":
+                            e["frac_of_copy_bandwidth"] = round(batch * seen(kv) * a.nkv * (a.hd + a.vd) * 2 / secs / 1e9 / pk["hbm_gbs"], 4)
+                        else:
+                            flops = sum(2 * a.nq * (a.hd + a.vd) * seen(k) for k in range(1, ctx + 1))
+                            e["frac_of_sustained_product_rate"] = round(flops / secs / (pk["bf16_tflops_sustained"] * 1e12), 4)
+                    kern[f"{kind}: {kname}"] = e
+            row[which] = {"layer_runs": len(called), "prefill_tok_s": round(ctx * 1000.0 / pre_ms, 1), "prefill_ms": round(pre_ms, 3),
+                          "decode_tok_s": round(dec["tok_s"], 1), "decode_ms_per_step": round(dec["ms"], 4),
+                          "decode_launches": dec["launches"], "weight_gb": round(model.weight_bytes() / 1e9, 2), "kernels": kern}
+            del model
+            torch.cuda.empty_cache()
+        out["sizes"][name] = row
+    return out
+
+
 def run_design_pair(args, pk, rng):
     """Prefill and decode of Puledra or Gepadra at layer sizes that resemble real models, beside Phi-MoE at equal width, heads
     and active expert parameters: tokens/s, and for the attention kernels of both the time a layer and the
@@ -923,9 +1051,9 @@ def main():
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the default run: decode at batch 1 and 8 with contexts of 16,384 and 65,536 tokens, "
                          "batch 1 with 131,008, and batch 128 and 256 with 2,048, each with its roofline fraction")
-    ap.add_argument("--design", choices=["puledra", "gepadra", "tefovik"], default=None,
+    ap.add_argument("--design", choices=["puledra", "gepadra", "tefovik", "dumizen"], default=None,
                     help="prefill and decode of this design at layer sizes that resemble real models, beside the closest "
-                         "earlier model at equal sizes (Phi-MoE; for tefovik Gepadra), with its kernels' shares of the peaks")
+                         "earlier model at equal sizes (Phi-MoE; for tefovik and dumizen Gepadra), with its kernels' shares of the peaks")
     ap.add_argument("--design-sizes", nargs="+", default=None, help="which of the design's size points to run")
     ap.add_argument("--profile", action="store_true",
                     help="print per-kernel device times of one prefill and one decode step to stderr and exit")
@@ -957,7 +1085,8 @@ def main():
         print(json.dumps(run_tiny(args.tiny)))
         return 0
     if args.design:
-        print(json.dumps(run_tefovik_pair(args, pk, rng) if args.design == "tefovik" else run_design_pair(args, pk, rng)))
+        run = {"tefovik": run_tefovik_pair, "dumizen": run_dumizen_pair}.get(args.design, run_design_pair)
+        print(json.dumps(run(args, pk, rng)))
         return 0
     if args.sweep:
         print(json.dumps(run_sweep(cfg, pk, rng, max(8, args.steps // 4), warmup)))

@@ -402,6 +402,11 @@ __device__ __forceinline__ void mma16816(float* d, const uint32_t* a, uint32_t b
 __device__ __forceinline__ void copy16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -537,16 +542,19 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
     if (sw.on) {
       // no softmax: a key's weight is sigmoid(cap tanh(score / cap) - r1 ln(1 + r2 distance) + bias), not normalised
       const float r1 = sw.r1 ? sw.r1[h] : 0.f, r2 = sw.r2 ? sw.r2[h] : 0.f, wb = sw.bias ? sw.bias[h] : 0.f;
+      const float inv_cap = sw.cap > 0.f ? 1.0f / sw.cap : 0.f;
 #pragma unroll
       for (int nt = 0; nt < MK / 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int j = kpos[nt * 8 + 2 * tq + (e & 1)], rs = e >> 1, p = p_row[rs];
           const bool ok = j >= 0 && row_ok[rs] && j <= p && (window == 0 || p - j < window);
+          // bfloat16 follows: the single-instruction forms of tanh and the logarithm will do, and
+          // sigmoid(x) = (1 + tanh(x / 2)) / 2
           float z = s[nt][e] * scale;
-          if (sw.cap > 0.f) z = sw.cap * (1.0f - 2.0f / (__expf(2.0f * z / sw.cap) + 1.0f));
-          if (sw.r1) z -= r1 * __logf(1.0f + r2 * (float)(p - j));
-          s[nt][e] = ok ? 1.0f / (1.0f + __expf(-(z + wb))) : 0.f;
+          if (sw.cap > 0.f) z = sw.cap * tanh_fast(z * inv_cap);
+          if (sw.r1) z -= r1 * __logf(fmaf(r2, (float)(p - j), 1.0f));
+          s[nt][e] = ok ? fmaf(0.5f, tanh_fast(0.5f * (z + wb)), 0.5f) : 0.f;
         }
     } else if (interior) {
 #pragma unroll

@@ -216,7 +216,9 @@ class CudaOps:
         _check(x, "x", torch.float32, 2)
         T, H = x.shape
         if H % 4 or H > 16384 or (router is not None and (row_index is not None or H * 4 > 160000
-                                                          or router.weight.shape[0] > H)):
+                                                          or router.weight.shape[0] > H
+                                                          or (getattr(router, "rule", "") == "sigmoid_grouped"
+                                                              and 2 * router.weight.shape[0] > H))):
             if pending is not None:
                 self.apply_pending(x, pending)
             tmp = out_f32
@@ -253,6 +255,7 @@ class CudaOps:
         E, jit, ids, gates = 0, 0.0, None, None
         r_top, r_groups, r_keep, r_scale = 0, 1, 1, 1.0
         r_rule, r_extra, r_aux = 0, 0, None
+        r_corr, r_norm = None, 0
         if router is not None:
             wr, E, jit, ids, gates = router.weight, router.weight.shape[0], router.jitter_eps, router.expert_ids, router.gates
             logits = getattr(router, "logits", None)
@@ -270,12 +273,16 @@ class CudaOps:
                 _check(r_aux, "router weights out", torch.float32, 2)
                 if tuple(r_aux.shape) != (T, r_top + r_extra) or r_top < 1:
                     raise KernelError(f"row_norm: the sigmoid router's weights must be [{T}, {r_top + r_extra}]")
+            elif getattr(router, "rule", "") == "sigmoid_grouped":
+                r_rule, r_corr, r_norm = 2, router.correction, 1 if router.normalize else 0
+                if r_corr is not None and (r_corr.dtype != torch.float32 or r_corr.numel() != E):
+                    raise KernelError("row_norm: the router's correction must be float32, one per expert")
         self._run("row_fused", "flint_row_norm", _ptr(x), _ptr(row_index), c_int(rows), c_int(H), _ptr(partials),
                   c_int(S), c_longlong(stride), _ptr(bias), _ptr(y), _ptr(row_of), _ptr(gts), c_int(top), _ptr(gamma), _ptr(beta),
                   c_float(eps), c_int({"layer": 0, "rms": 1}[mode]), _ptr(out_f32), _ptr(out_bf16), _ptr(wr),
                   c_int(_code(wr.dtype) if wr is not None else 0), c_int(E), c_float(jit), _ptr(ids), _ptr(gates),
                   _ptr(logits), c_int(r_top), c_int(r_groups), c_int(r_keep), c_float(r_scale), c_int(r_rule), c_int(r_extra),
-                  _ptr(r_aux))
+                  _ptr(r_aux), _ptr(r_corr), c_int(r_norm))
 
     def apply_pending(self, x, pending):
         """x += what a part left pending (for a norm that cannot take it along)."""
@@ -809,6 +816,7 @@ class CudaOps:
         _check(q, "q", dims=2)
         _check(out, "out", q.dtype, 2)
         cap, r1, r2, w_bias = sigmoid if sigmoid is not None else (0.0, None, None, None)
+        kind = "sigmoid" if sigmoid is not None else ("pooled" if pool else "softmax")     # profiles list the launches by it
         for name, t in (("r1", r1), ("r2", r2), ("bias", w_bias)):
             if t is not None and (t.dtype != torch.float32 or t.numel() != nq):
                 raise KernelError(f"sink_attention: {name} must be float32 [{nq}]")
@@ -829,6 +837,7 @@ class CudaOps:
         if (tiling is not None and tiling.n_tiles > 0 and rows is None and splits is None
                 and self.sink_attention_tiles_ok(q.dtype, cache.k.dtype, hd, vd)):
             _check(tiling.tiles, "tiles", torch.int32)
+            self._label = kind
             self._run("attention_sink", "flint_sink_attention_tiles", _ptr(q), _ptr(cache.k), _ptr(cache.v),
                       _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(P), _ptr(tiling.tiles),
                       c_int(tiling.n_tiles), _ptr(out), c_int(nq), c_int(nkv), c_int(hd), c_int(vd), c_int(window),
@@ -850,6 +859,7 @@ class CudaOps:
         if keys * n < span:
             raise KernelError(f"sink_attention: {n} splits of {keys} keys do not cover {span} keys")
         scratch = torch.empty(T * nq * n * (vd + 2), dtype=torch.float32, device=q.device) if n > 1 else None
+        self._label = kind
         self._run("attention_sink", "flint_sink_attention", _ptr(q), c_int(_code(q.dtype)), _ptr(cache.k), _ptr(cache.v),
                   c_int(_code(cache.k.dtype)), _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(P),
                   _ptr(step.pos), _ptr(step.slot), _ptr(out), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(vd),
@@ -1375,6 +1385,10 @@ class CudaOps:
         if getattr(router, "rule", "") == "sigmoid":
             return self.router_sigmoid(x, router.weight, router.weight.shape[0] - router.extra, router.top, router.expert_ids,
                                        router.gates, router.weights, getattr(router, "logits", None))
+        if getattr(router, "rule", "") == "sigmoid_grouped":
+            return self.router_sigmoid_grouped(x, router.weight, router.correction, router.top, router.groups, router.keep,
+                                               router.normalize, router.scale, router.expert_ids, router.gates,
+                                               getattr(router, "logits", None))
         if int(getattr(router, "top", 0)) > 0:
             return self.router_topk(x, router.weight, router.top, router.groups, router.keep, router.scale,
                                     router.expert_ids, router.gates, getattr(router, "logits", None))

@@ -347,15 +347,40 @@ __global__ void sum_norm_add_kernel(SumList sl, const float* __restrict__ gamma,
       r = fmaf(sl.gates[(size_t)t * sl.k + j], sl.y[(size_t)sl.row_of[(size_t)t * sl.k + j] * W + c], r);
     return r;
   };
+  constexpr int KEEP = 8;      // values a thread keeps between the two passes (rows up to KEEP x the block's threads)
+  const bool kept = W <= KEEP * (int)blockDim.x;
+  float v[KEEP];
   float inv = 1.f;
-  if (gamma) {
+  if (gamma || kept) {
     float ss = 0.f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-      const float x = value(c);
-      ss = fmaf(x, x, ss);
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      v[i] = kept && c < W ? value(c) : 0.f;
+      ss = fmaf(v[i], v[i], ss);
     }
-    ss = block_sum(ss, red);
-    inv = 1.0f / sqrtf(ss / (float)W + eps);
+    if (!kept)
+      for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float x = value(c);
+        ss = fmaf(x, x, ss);
+      }
+    if (gamma) {
+      ss = block_sum(ss, red);
+      inv = 1.0f / sqrtf(ss / (float)W + eps);
+    }
+  }
+  if (kept) {
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < W) {
+        float r = v[i] * inv;
+        if (gamma) r *= gamma[c];
+        float* d = dst + (size_t)t * W + c;
+        *d = accumulate ? *d + r : r;
+      }
+    }
+    return;
   }
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
     float r = value(c) * inv;

@@ -33,6 +33,7 @@ struct RowArgs {
   const void* wr; int E; float jitter_eps; int* expert_ids; float* gates;
   int top, n_groups, keep; float out_scale;      // top > 0: the softmax router limited to groups instead of sparsemixer
   int rule, extra; float* aux;  // rule 1: the sigmoid router (scores into gates, the last `extra` rows of wr are gates: aux)
+  const float* correction; int normalize;   // rule 2: the sigmoid router limited to groups (select_sigmoid_grouped_by_warp)
   float* router_logits;        // optional [rows, E]: the logits the selection was made from (for tests)
   int H;
 };
@@ -280,7 +281,10 @@ row_norm_kernel(const __grid_constant__ RowArgs a) {
       if (a.router_logits) a.router_logits[(size_t)r * E + e] = t;
     }
     __syncwarp();
-    if (a.rule == 1)
+    if (a.rule == 2)
+      select_sigmoid_grouped_by_warp(s, s + E, a.correction, lane, E, a.top, a.n_groups, a.keep, a.normalize, a.out_scale,
+                                     a.expert_ids + (size_t)a.top * r, a.gates + (size_t)a.top * r);
+    else if (a.rule == 1)
       select_sigmoid_by_warp(s, lane, E - a.extra, a.extra, a.top, a.expert_ids + (size_t)a.top * r,
                              a.gates + (size_t)a.top * r, a.aux + (size_t)(a.top + a.extra) * r);
     else
@@ -527,7 +531,10 @@ row_norm_cluster_kernel(const __grid_constant__ RowArgs a, const int vec_per_blo
       if (a.router_logits) a.router_logits[(size_t)r * E + e] = t;
     }
     __syncwarp();
-    if (a.rule == 1)
+    if (a.rule == 2)
+      select_sigmoid_grouped_by_warp(s, s + E, a.correction, lane, E, a.top, a.n_groups, a.keep, a.normalize, a.out_scale,
+                                     a.expert_ids + (size_t)a.top * r, a.gates + (size_t)a.top * r);
+    else if (a.rule == 1)
       select_sigmoid_by_warp(s, lane, E - a.extra, a.extra, a.top, a.expert_ids + (size_t)a.top * r,
                              a.gates + (size_t)a.top * r, a.aux + (size_t)(a.top + a.extra) * r);
     else
@@ -608,14 +615,18 @@ extern "C" int flint_row_norm_set_cluster_rows(int rows) {
 // must be NULL.  top > 0: the router is a softmax limited to groups (`keep` of `n_groups`, `top` experts, gates times
 // out_scale) and expert_ids and gates are [rows, top]; top == 0: sparsemixer top-2.  rule 1: a sigmoid router over the
 // first E - extra rows of wr (the `top` largest scores, given as they are in gates); the last `extra` rows are gates of
-// always-on parts, and aux [rows, top + extra] gets 1 for the chosen experts and those rows' sigmoids.
+// always-on parts, and aux [rows, top + extra] gets 1 for the chosen experts and those rows' sigmoids.  rule 2: a sigmoid
+// router limited to groups: choice scores sigmoid + correction [E] (or NULL), a group scores as the sum of its two
+// largest, `top` experts of the `keep` best of `n_groups` groups; gates the chosen sigmoids, over their sum if
+// `normalize`, times out_scale.
 extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, const float* partials,
                               int n_partials, long long partial_stride, const float* add_bias,
                               const float* comb_y, const int* comb_row_of, const float* comb_gates, int comb_top,
                               const float* gamma, const float* beta, float eps, int mode, float* out_f32,
                               void* out_bf16, const void* wr, int w_dtype, int E, float jitter_eps,
                               int* expert_ids, float* gates, float* router_logits, int top, int n_groups, int keep,
-                              float out_scale, int rule, int extra, float* aux, cudaStream_t stream) {
+                              float out_scale, int rule, int extra, float* aux, const float* correction, int normalize,
+                              cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (H <= 0 || (H & 3) || H > 4 * 1024 * MAX_VPT) return fail("row_norm: width %d (multiples of 4 up to %d)", H, 4096 * MAX_VPT);
   if (gamma && !out_f32 && !out_bf16 && !wr) return fail("row_norm: no output given");
@@ -625,8 +636,10 @@ extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, c
   if (wr && rule == 1) {
     if (top < 1 || top > ROUTER_MAX_TOP || extra < 0 || top > E - extra || !aux)
       return fail("row_norm: a sigmoid router choosing %d of %d experts (%d gate rows) is not supported", top, E - extra, extra);
-  } else if (wr && rule != 0) {
+  } else if (wr && rule != 0 && rule != 2) {
     return fail("row_norm: unknown router rule %d", rule);
+  } else if (wr && rule == 2 && (top < 1 || 2 * E > H)) {
+    return fail("row_norm: the grouped sigmoid router needs top >= 1 and rows of at least twice the %d experts", E);
   } else if (wr && top > 0 && (top > ROUTER_MAX_TOP || top > E || n_groups < 1 || n_groups > 64 || E % n_groups || keep < 1 ||
                         keep > n_groups || keep * (E / n_groups) < top))
     return fail("row_norm: %d of %d experts from %d of %d groups is not supported", top, E, keep, n_groups);
@@ -642,6 +655,7 @@ extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, c
   a.top = wr ? top : 0; a.n_groups = n_groups; a.keep = keep; a.out_scale = out_scale;
   a.router_logits = wr ? router_logits : nullptr;
   a.rule = wr ? rule : 0; a.extra = extra; a.aux = aux;
+  a.correction = correction; a.normalize = normalize;
   a.H = H;
   const int n4 = H / 4;
   // a handful of rows: a cluster of blocks per row
@@ -656,7 +670,7 @@ extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, c
     const int n_warps = threads / 32;
     const int groups = (E + 3) / 4;
     const int k = wr ? (n_warps >= groups ? n_warps / groups : 1) : 0;
-    const size_t smem = wr ? (size_t)(4 * vec_per_block + E * k + MAX_CL * E + E) * sizeof(float) : 0;
+    const size_t smem = wr ? (size_t)(4 * vec_per_block + E * k + MAX_CL * E + 2 * E) * sizeof(float) : 0;
     if (smem <= 48 * 1024 && vpt <= MAX_VPT) {
 #define GOC(V) (wr && w_dtype == FLINT_BF16 ? launch_row_cluster<V, __nv_bfloat16>(a, rows, cl, vec_per_block, threads, smem, stream) \
                                             : launch_row_cluster<V, float>(a, rows, cl, vec_per_block, threads, smem, stream))

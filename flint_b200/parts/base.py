@@ -60,7 +60,10 @@ class RouterRequest:
     the ``keep`` best of ``groups`` equal groups of neighbouring experts, ``top`` experts a token, gates times
     ``scale``.  With ``rule`` "sigmoid": scores sigmoid(logit) over the first rows of ``weight``, the ``top`` largest
     chosen, ``gates`` their scores as they are; the last ``extra`` rows of ``weight`` are gates of always-on parts,
-    and ``weights`` [T, top + extra] gets 1 for every chosen expert and those rows' sigmoids.  ``logits`` ([T, E]
+    and ``weights`` [T, top + extra] gets 1 for every chosen expert and those rows' sigmoids.  With ``rule``
+    "sigmoid_grouped": choice scores sigmoid(logit) + ``correction`` [E] (or None), a group of neighbouring experts scores
+    as the sum of its two largest choice scores, ``top`` experts of the ``keep`` best of ``groups`` groups are chosen,
+    ``gates`` their sigmoids, over their sum if ``normalize``, times ``scale``.  ``logits`` ([T, E]
     float32, optional): the logits the choice was made from are written there too (tests compare them)."""
     weight: torch.Tensor
     jitter_eps: float
@@ -74,6 +77,8 @@ class RouterRequest:
     rule: str = ""
     extra: int = 0
     weights: torch.Tensor | None = None
+    correction: torch.Tensor | None = None
+    normalize: bool = True
 
 
 @dataclass

@@ -338,7 +338,11 @@ class SigmoidTopKMoE(FeedForward):
     def router_request(self, n_rows):
         """Routing can ride on the norm before this part (the normalised row is in registers there)."""
         if self.weighting == "output":
-            return None          # the grouped rule runs as a kernel of its own
+            dev, k = self.w_router.device, self.top
+            return RouterRequest(self.w_router, 0.0, torch.empty((n_rows, k), dtype=torch.int32, device=dev),
+                                 torch.empty((n_rows, k), dtype=torch.float32, device=dev), top=k, groups=self.groups,
+                                 keep=self.keep, scale=self.router_scale, rule="sigmoid_grouped",
+                                 correction=self.w_correction, normalize=self.normalize)
         dev, k, extra = self.w_router.device, self.top, 1 if self.shared else 0
         return RouterRequest(self.w_router, 0.0, torch.empty((n_rows, k), dtype=torch.int32, device=dev),
                              torch.empty((n_rows, k), dtype=torch.float32, device=dev), top=k, rule="sigmoid", extra=extra,
@@ -352,7 +356,7 @@ class SigmoidTopKMoE(FeedForward):
         xa = x[self.w_up.dtype]
         T, dev, k, extra = xa.shape[0], xa.device, self.top, 1 if self.shared else 0
         if self.weighting == "output":
-            return self._forward_output_weighted(x, xa, step)
+            return self._forward_output_weighted(x, xa, step, routed)
         if routed is not None:
             # what the pending rows are weighted by when they are added: 1 for the experts (their score went into
             # their input), the sigmoid gate for the shared expert
@@ -381,17 +385,20 @@ class SigmoidTopKMoE(FeedForward):
             step.record.setdefault("router_logits", []).append(logits)
         return Pending(y=y, row_of=row_of, gates=weights)
 
-    def _forward_output_weighted(self, x, xa, step):
+    def _forward_output_weighted(self, x, xa, step, routed=None):
         """The chosen experts' outputs times their weights, and the shared expert's output as one more row a token
         with weight 1."""
         ops = self.ops
         T, dev, k, extra = xa.shape[0], xa.device, self.top, 1 if self.shared else 0
-        ids = torch.empty((T, k), dtype=torch.int32, device=dev)
-        weights = torch.empty((T, k + extra), dtype=torch.float32, device=dev)
-        logits = torch.empty((T, self.E), dtype=torch.float32, device=dev) if step.record is not None else None
-        gates = weights[:, :k] if not extra else torch.empty((T, k), dtype=torch.float32, device=dev)
-        ops.router_sigmoid_grouped(x[torch.float32], self.w_router, self.w_correction, k, self.groups, self.keep,
-                                   self.normalize, self.router_scale, ids, gates, logits)
+        if routed is not None:          # the norm before this part chose while it had the row
+            ids, gates, logits = routed.expert_ids, routed.gates, routed.logits
+        else:
+            ids = torch.empty((T, k), dtype=torch.int32, device=dev)
+            gates = torch.empty((T, k), dtype=torch.float32, device=dev)
+            logits = torch.empty((T, self.E), dtype=torch.float32, device=dev) if step.record is not None else None
+            ops.router_sigmoid_grouped(x[torch.float32], self.w_router, self.w_correction, k, self.groups, self.keep,
+                                       self.normalize, self.router_scale, ids, gates, logits)
+        weights = gates
         plan, xs = ops.moe_dispatch(ids, self.E, ops.moe_tile_rows(T, self.E, self.w_up.dtype, k), xa)
         a = torch.empty((k * T, self.inter), dtype=self.w_up.dtype, device=dev)
         ops.row_act(ops.gemm_partials(xs, self.w_up, plan=plan), a, self.act)

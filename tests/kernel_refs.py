@@ -72,7 +72,11 @@ class RefOps:
             tmp = torch.empty((x.shape[0], x.shape[1]), dtype=torch.float32)
         self.norm(x, gamma, beta, eps, mode, out_f32=tmp, out_bf16=out_bf16, row_index=row_index)
         if router is not None:
-            if getattr(router, "rule", "") == "sigmoid":
+            if getattr(router, "rule", "") == "sigmoid_grouped":
+                self.router_sigmoid_grouped(tmp, router.weight, router.correction, router.top, router.groups, router.keep,
+                                            router.normalize, router.scale, router.expert_ids, router.gates,
+                                            getattr(router, "logits", None))
+            elif getattr(router, "rule", "") == "sigmoid":
                 self.router_sigmoid(tmp, router.weight, router.weight.shape[0] - router.extra, router.top, router.expert_ids,
                                     router.gates, router.weights, getattr(router, "logits", None))
             elif int(getattr(router, "top", 0)) > 0:

@@ -501,3 +501,29 @@ def test_trace_run_as_a_program(setup, tmp_path, dtype):
         assert float(errs.max()) < 1e-4
     else:       # a near-tie of two choice scores may fall the other way at some rows
         assert float(errs.median()) < 4e-2
+
+
+@pytest.mark.parametrize("T,W", [(1, 192), (8, 2048), (16, 4096), (300, 200), (2048, 1024)])
+@pytest.mark.parametrize("E,top,groups,keep", [(12, 3, 2, 1), (64, 6, 8, 3), (16, 2, 4, 2)])
+def test_the_grouped_sigmoid_router_rides_on_the_norm(ops, T, W, E, top, groups, keep):
+    """The norm's kernel (a block a row, a cluster a row, many rows) chooses while it has the normalised row: its
+    choice is exactly the rule applied to the logits it reports, and those agree with the plain product."""
+    from flint_b200.parts.base import RouterRequest
+    g = torch.Generator().manual_seed(T + E)
+    x = torch.randn(T, W, generator=g)
+    gamma = 1 + 0.1 * torch.randn(W, generator=g)
+    wr = (2.5 * torch.randn(E, W, generator=g) / math.sqrt(W)).to(torch.bfloat16)
+    corr = 0.3 * torch.randn(E, generator=g)
+    req = RouterRequest(wr.to(DEV), 0.0, torch.zeros(T, top, dtype=torch.int32, device=DEV), torch.zeros(T, top, device=DEV),
+                        logits=torch.zeros(T, E, device=DEV), top=top, groups=groups, keep=keep, scale=2.5, rule="sigmoid_grouped",
+                        correction=corr.to(DEV), normalize=True)
+    out = torch.zeros(T, W, dtype=torch.bfloat16, device=DEV)
+    ops.row_norm(x.to(DEV), gamma.to(DEV), None, 1e-6, "rms", out_bf16=out, router=req)
+    normed = x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + 1e-6) * gamma.double()
+    assert (req.logits.cpu().double() - normed @ wr.double().T).abs().max() < 1e-4
+    ids_r, gates_r = torch.zeros(T, top, dtype=torch.int32), torch.zeros(T, top, dtype=F64)
+    # the rule on the kernel's own logits: x = logits, the router's matrix the identity
+    RefOps(F64).router_sigmoid_grouped(req.logits.cpu().double(), torch.eye(E, dtype=F64), corr, top, groups, keep, True, 2.5, ids_r, gates_r)
+    same = (ids_r == req.expert_ids.cpu()).all(-1)
+    assert int((~same).sum()) <= max(1, T // 500)
+    assert (gates_r[same] - req.gates.cpu().double()[same]).abs().max() < 1e-5
