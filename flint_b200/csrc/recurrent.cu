@@ -347,46 +347,83 @@ __global__ void sum_norm_add_kernel(SumList sl, const float* __restrict__ gamma,
       r = fmaf(sl.gates[(size_t)t * sl.k + j], sl.y[(size_t)sl.row_of[(size_t)t * sl.k + j] * W + c], r);
     return r;
   };
-  constexpr int KEEP = 8;      // values a thread keeps between the two passes (rows up to KEEP x the block's threads)
-  const bool kept = W <= KEEP * (int)blockDim.x;
-  float v[KEEP];
   float inv = 1.f;
-  if (gamma || kept) {
+  if (gamma) {
     float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < KEEP; ++i) {
-      const int c = threadIdx.x + i * blockDim.x;
-      v[i] = kept && c < W ? value(c) : 0.f;
-      ss = fmaf(v[i], v[i], ss);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      const float x = value(c);
+      ss = fmaf(x, x, ss);
     }
-    if (!kept)
-      for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float x = value(c);
-        ss = fmaf(x, x, ss);
-      }
-    if (gamma) {
-      ss = block_sum(ss, red);
-      inv = 1.0f / sqrtf(ss / (float)W + eps);
-    }
-  }
-  if (kept) {
-#pragma unroll
-    for (int i = 0; i < KEEP; ++i) {
-      const int c = threadIdx.x + i * blockDim.x;
-      if (c < W) {
-        float r = v[i] * inv;
-        if (gamma) r *= gamma[c];
-        float* d = dst + (size_t)t * W + c;
-        *d = accumulate ? *d + r : r;
-      }
-    }
-    return;
+    ss = block_sum(ss, red);
+    inv = 1.0f / sqrtf(ss / (float)W + eps);
   }
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
     float r = value(c) * inv;
     if (gamma) r *= gamma[c];
     float* d = dst + (size_t)t * W + c;
     *d = accumulate ? *d + r : r;
+  }
+}
+
+// The same with rows of whole 16-byte units, every pointer on 16 bytes: a thread holds up to four units of the row in
+// registers between the sum of squares and the store, so the row's operands are read once and the blocks are small
+// enough that several share an SM.
+__global__ void sum_norm_add_vec_kernel(SumList sl, const float* __restrict__ gamma, float eps, float* __restrict__ dst,
+                                        int accumulate, int W) {
+  __shared__ float red[32];
+  pdl_launch();
+  pdl_wait();
+  constexpr int U = 4;
+  const int t = blockIdx.x, n4 = W / 4;
+  float4 v[U];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < U; ++i) {
+    const int c4 = threadIdx.x + i * blockDim.x;
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c4 < n4) {
+      for (int b = 0; b < sl.n; ++b) {
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int z = 0; z < sl.n_partials[b]; ++z) {
+          const float4 q = *reinterpret_cast<const float4*>(sl.partials[b] + (size_t)z * sl.stride[b] + (size_t)t * W + 4 * c4);
+          x.x += q.x; x.y += q.y; x.z += q.z; x.w += q.w;
+        }
+        if (sl.bias[b]) {
+          const float4 q = *reinterpret_cast<const float4*>(sl.bias[b] + 4 * c4);
+          x.x += q.x; x.y += q.y; x.z += q.z; x.w += q.w;
+        }
+        const float sc = sl.scale[b];
+        r.x = fmaf(sc, x.x, r.x); r.y = fmaf(sc, x.y, r.y); r.z = fmaf(sc, x.z, r.z); r.w = fmaf(sc, x.w, r.w);
+      }
+      for (int j = 0; j < sl.k; ++j) {
+        const float gt = sl.gates[(size_t)t * sl.k + j];
+        const float4 q = *reinterpret_cast<const float4*>(sl.y + (size_t)sl.row_of[(size_t)t * sl.k + j] * W + 4 * c4);
+        r.x = fmaf(gt, q.x, r.x); r.y = fmaf(gt, q.y, r.y); r.z = fmaf(gt, q.z, r.z); r.w = fmaf(gt, q.w, r.w);
+      }
+    }
+    v[i] = r;
+    ss = fmaf(r.x, r.x, fmaf(r.y, r.y, fmaf(r.z, r.z, fmaf(r.w, r.w, ss))));
+  }
+  float inv = 1.f;
+  if (gamma) {
+    ss = block_sum(ss, red);
+    inv = 1.0f / sqrtf(ss / (float)W + eps);
+  }
+#pragma unroll
+  for (int i = 0; i < U; ++i) {
+    const int c4 = threadIdx.x + i * blockDim.x;
+    if (c4 >= n4) continue;
+    float4 r = v[i];
+    if (gamma) {
+      const float4 gm = *reinterpret_cast<const float4*>(gamma + 4 * c4);
+      r.x *= inv * gm.x; r.y *= inv * gm.y; r.z *= inv * gm.z; r.w *= inv * gm.w;
+    }
+    float4* d = reinterpret_cast<float4*>(dst + (size_t)t * W + 4 * c4);
+    if (accumulate) {
+      const float4 o = *d;
+      r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w;
+    }
+    *d = r;
   }
 }
 
@@ -769,7 +806,16 @@ extern "C" int flint_sum_norm_add(int n, const float* const* partials, const lon
     sl.scale[b] = scales[b];
   }
   sl.y = y; sl.row_of = row_of; sl.gates = gates; sl.k = k;
-  launch_pdl(sum_norm_add_kernel, dim3((unsigned)T), dim3(row_threads(W)), 0, stream, sl, gamma, eps, dst, accumulate, W);
+  bool vec = W % 4 == 0 && W <= 4 * 4 * 1024 && !(((uintptr_t)dst | (uintptr_t)gamma | (uintptr_t)y) & 15);
+  for (int b = 0; b < n && vec; ++b)
+    vec = !(((uintptr_t)partials[b] | (uintptr_t)bias[b]) & 15) && strides[b] % 4 == 0;
+  if (vec) {
+    int threads = ((W / 16 + 31) / 32) * 32;          // four 16-byte units a thread
+    if (threads < 64) threads = 64;
+    launch_pdl(sum_norm_add_vec_kernel, dim3((unsigned)T), dim3(threads), 0, stream, sl, gamma, eps, dst, accumulate, W);
+  } else {
+    launch_pdl(sum_norm_add_kernel, dim3((unsigned)T), dim3(row_threads(W)), 0, stream, sl, gamma, eps, dst, accumulate, W);
+  }
   return check_launch("sum_norm_add");
 }
 

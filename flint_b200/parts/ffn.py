@@ -386,8 +386,8 @@ class SigmoidTopKMoE(FeedForward):
         return Pending(y=y, row_of=row_of, gates=weights)
 
     def _forward_output_weighted(self, x, xa, step, routed=None):
-        """The chosen experts' outputs times their weights, and the shared expert's output as one more row a token
-        with weight 1."""
+        """The chosen experts' outputs as rows with their weights, and the shared expert's output as the partial sums
+        of its down product: whoever adds them (the kernel after the part) adds both."""
         ops = self.ops
         T, dev, k, extra = xa.shape[0], xa.device, self.top, 1 if self.shared else 0
         if routed is not None:          # the norm before this part chose while it had the row
@@ -398,26 +398,18 @@ class SigmoidTopKMoE(FeedForward):
             logits = torch.empty((T, self.E), dtype=torch.float32, device=dev) if step.record is not None else None
             ops.router_sigmoid_grouped(x[torch.float32], self.w_router, self.w_correction, k, self.groups, self.keep,
                                        self.normalize, self.router_scale, ids, gates, logits)
-        weights = gates
         plan, xs = ops.moe_dispatch(ids, self.E, ops.moe_tile_rows(T, self.E, self.w_up.dtype, k), xa)
         a = torch.empty((k * T, self.inter), dtype=self.w_up.dtype, device=dev)
         ops.row_act(ops.gemm_partials(xs, self.w_up, plan=plan), a, self.act)
-        y = torch.empty(((k + extra) * T, self.hidden), dtype=torch.float32, device=dev)
-        ops.grouped_gemm(a, self.w_down, y[:k * T], plan, plan_ready=True)
-        row_of = plan.row_of
-        if self.shared:
+        y = torch.empty((k * T, self.hidden), dtype=torch.float32, device=dev)
+        ops.grouped_gemm(a, self.w_down, y, plan, plan_ready=True)
+        shared = None
+        if self.shared:          # added as it is: its down product travels as partial sums beside the experts' rows
             b = torch.empty((T, self.shared), dtype=self.w_up.dtype, device=dev)
             ops.row_act(ops.gemm_partials(xa, self.w_sup), b, self.act)
-            ops.gemm(b, self.w_sdown, y[k * T:])
-            row_of, weights = self._with_shared_row(row_of, gates, T, k, dev)
+            shared = ops.gemm_partials(b, self.w_sdown)
         if step.record is not None:
             step.record.setdefault("experts", []).append(ids)
             step.record.setdefault("gates", []).append(gates)
             step.record.setdefault("router_logits", []).append(logits)
-        return Pending(y=y, row_of=row_of, gates=weights)
-
-    def _with_shared_row(self, row_of, gates, T, k, dev):
-        """(row_of, weights) with one more column: the shared expert's row of every token, weight 1."""
-        own = torch.arange(k * T, (k + 1) * T, dtype=torch.int32, device=dev)
-        return (torch.cat([row_of, own[:, None]], 1).contiguous(),
-                torch.cat([gates, torch.ones((T, 1), dtype=torch.float32, device=dev)], 1).contiguous())
+        return Pending(partials=shared, y=y, row_of=plan.row_of, gates=gates)

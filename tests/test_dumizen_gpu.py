@@ -269,11 +269,7 @@ def test_the_norm_and_rotation_kernel_in_its_new_forms(ops, dtype, whole, v_from
     assert (c_dev.k.cpu().double() - c_ref.k.double()).abs().max() < tol and (c_dev.v.cpu().double() - c_ref.v.double()).abs().max() < tol
 
 
-def test_the_small_kernels_beside_their_references(ops):
-    g = torch.Generator().manual_seed(5)
-    ref = RefOps(F64)
-    # weighted sums of branches and expert rows, normed and added
-    T, W = 37, 200
+def _sum_norm_add_case(ops, ref, g, T, W):
     parts = [torch.randn(3, T, W, generator=g), torch.randn(1, T, W, generator=g)]
     bias = torch.randn(W, generator=g)
     y, gates = torch.randn(3 * T, W, generator=g), torch.rand(T, 3, generator=g)
@@ -291,6 +287,14 @@ def test_the_small_kernels_beside_their_references(ops):
         ref.sum_norm_add(a, **kw_cpu)
         ops.sum_norm_add(b, **{k: dev(v) for k, v in kw_cpu.items()})
         assert (b.cpu().double() - a).abs().max() < 2e-5
+
+
+def test_the_small_kernels_beside_their_references(ops):
+    g = torch.Generator().manual_seed(5)
+    ref = RefOps(F64)
+    # weighted sums of branches and expert rows, normed and added (rows of whole 16-byte units and not, a wide row)
+    for T, W in ((37, 200), (37, 203), (5, 4096)):
+        _sum_norm_add_case(ops, ref, g, T, W)
     # retention's rotated q and k, its constant decays and step sizes
     H, D, T = 3, 10, 29
     proj = torch.randn(T, 2 * H * D + 17, generator=g)
