@@ -24,10 +24,6 @@ def norm(x, g, eps):
     return rms(x, eps) * g
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 # ------------------------------------------------------------------------------------------------ rotation
 def rotary_frequencies(rot):
     """(frequencies [dims/2], factor on cos and sin) of a ``rot`` section; YaRN if it has ``scaling``."""

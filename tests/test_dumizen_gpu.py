@@ -507,11 +507,12 @@ def test_trace_run_as_a_program(setup, tmp_path, dtype):
         assert float(errs.median()) < 4e-2
 
 
-@pytest.mark.parametrize("T,W", [(1, 192), (8, 2048), (16, 4096), (300, 200), (2048, 1024)])
+@pytest.mark.parametrize("T,W", [(1, 192), (8, 2048), (16, 4096), (300, 200), (2048, 1024), (40, 72)])
 @pytest.mark.parametrize("E,top,groups,keep", [(12, 3, 2, 1), (64, 6, 8, 3), (16, 2, 4, 2)])
 def test_the_grouped_sigmoid_router_rides_on_the_norm(ops, T, W, E, top, groups, keep):
     """The norm's kernel (a block a row, a cluster a row, many rows) chooses while it has the normalised row: its
-    choice is exactly the rule applied to the logits it reports, and those agree with the plain product."""
+    choice is exactly the rule applied to the logits it reports, and those agree with the plain product.  Rows narrower
+    than twice the experts go to the norm and the stand-alone router one after the other."""
     from flint_b200.parts.base import RouterRequest
     g = torch.Generator().manual_seed(T + E)
     x = torch.randn(T, W, generator=g)
