@@ -126,14 +126,14 @@ def _heads(m, where, values_are_keys=False):
     vdim = F.get_int(m, "vdim", dim if values_are_keys else F._MISSING, minimum=1)
     if values_are_keys and vdim != dim:
         raise ConfigError(f"{where}: the values are the keys, so vdim {vdim} must equal dim {dim}")
-    return Heads(heads, kv, dim, vdim, F.get_float(m, "scale"), _rotation(m, dim, where))
+    return Heads(heads, kv, dim, vdim, F.get_float(m, "scale", dim ** -0.5), _rotation(m, dim, where))
 
 
 def _mixer(kind, m, where):
     if kind == "attention":
         mask = _section(m, "mask", optional=True)
         window = F.get_int(mask, "size", minimum=1) if mask is not None else 0
-        pool = F.get_int(mask, "pool", minimum=1) if mask is not None else 0
+        pool = F.get_int(mask, "pool", 0, minimum=0) if mask is not None else 0       # 0: a plain window
         return PooledWindowAttention(_heads(m, where), window, pool)
     if kind == "attention_2":
         qt = _section(m, "q_temp", optional=True)

@@ -76,9 +76,10 @@ def pooled_window_attention(h, w, pre, m, eps):
     mask = m.get("mask")
     i, j = pos[:, None], pos[None, :]
     if mask:
-        size, P = int(mask["size"]), int(mask["pool"])
+        size, P = int(mask["size"]), int(mask.get("pool") or 0)
         seen = (i - j >= 0) & (i - j < size)
-        nb = T // P
+        nb = T // P if P else 0            # without a block size: the window alone
+        P = P or 1
         kp = k[:nb * P].view(nb, P, G, D).mean(1)
         vp = v[:nb * P].view(nb, P, G, V).mean(1)
         b = torch.arange(nb)[None, :]

@@ -268,3 +268,22 @@ def test_greedy_generation_through_the_engine_with_preemption(setup):
         assert eng.generate(prompts, 10) == expected
         assert all(g.pages.pool.used_pages == 0 for g in m.cache.groups) and m.cache.free_slots == 4
     assert eng.scheduler.preemptions > 0
+
+
+def test_a_window_without_blocks_gives_its_pages_back(tmp_path):
+    """A mask that names no block size is a plain window: nothing behind it is seen, and the pages behind it go
+    back to the pool while the request runs."""
+    cfg = copy.deepcopy(tiny.D3)
+    cfg["layers"] = [cfg["layers"][2]]
+    del cfg["layers"][0]["mixer"]["mask"]["pool"]
+    folder, w = tiny.write_model(tmp_path / "m", cfg, seed=3)
+    reqs = traces.make_requests(cfg["vocab"], (70, 9), seed=7)
+    plain = {rid: P.forward(cfg, w, t)[0] for rid, t in reqs.items()}
+    steps = traces.portions(reqs, sizes=(7, 2, 13, 3))
+    out, _, rp = replay(folder, steps)
+    compare(out, steps, plain)
+    spec = rp.model.cache.groups[0].spec
+    assert spec.window == 10 and spec.pool == 0
+    rp2 = Replayer(folder, dtype="float32", max_tokens=128, page_size=16, max_requests=1, device="cpu", ops=RefOps())
+    rp2.run_step([{"id": "a", "tokens": reqs["r0"][:60], "want": []}])
+    assert rp2.model.cache.groups[0].pages.pool.used_pages <= 2        # 60 positions would hold four pages of 16

@@ -532,3 +532,28 @@ def test_the_grouped_sigmoid_router_rides_on_the_norm(ops, T, W, E, top, groups,
     same = (ids_r == req.expert_ids.cpu()).all(-1)
     assert int((~same).sum()) <= max(1, T // 500)
     assert (gates_r[same] - req.gates.cpu().double()[same]).abs().max() < 1e-5
+
+
+def test_chat_program_with_random_weights(tmp_path):
+    """bin/flint_chat with ``--random-config FILE --seed N``, token ids in and out, greedy: the tokens of the folder
+    that the random-weights mode writes for that configuration and seed, under the plain implementation."""
+    from flint_b200.engine.loading import write_random_model
+    from flint_b200.weights.safetensors_io import SafetensorsFile
+    seed, cfg = 4, tiny.D1
+    folder = write_random_model(tmp_path / "model", cfg, seed=seed)
+    f = SafetensorsFile(folder / "model.safetensors")
+    w = {n: f.read(n).double() for n in f.names()}
+    prompt = [3, 50, 50, 7, 80, 0, 12, 13, 14, 15, 16]
+    cfg_file = tmp_path / "only_config.json"
+    cfg_file.write_text(json.dumps(cfg))
+    proc = subprocess.run([sys.executable, f"{REPO}/bin/flint_chat", "--random-config", str(cfg_file), "--prompt", " ".join(map(str, prompt)),
+                           "--max-tokens", "8", "--temperature", "0", "--seed", str(seed), "--dtype", "float32", "--ctx-size", "128"],
+                          capture_output=True, text=True, timeout=600, env={**os.environ, "VERIFY_IDS": "1"})
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    got = [int(x) for x in proc.stdout.split()]
+    toks, want = list(prompt), []
+    for _ in range(8):
+        t = int(torch.argmax(P.forward(cfg, w, toks)[0][-1]))
+        want.append(t)
+        toks.append(t)
+    assert got == want
